@@ -6,7 +6,8 @@ writes a cache) whose needs are equal form a *group*; each group has its own poo
 has one block table per group (logical page i -> physical page id, -1 where nothing is held).  One page id of
 a group covers all units of that group, as one block id covers all layers in the reference
 (engine/model_runner.cpp:104-113).  A group whose mixers look back only ``window`` positions gives a page back
-as soon as every position in it lies before the window of the request's next token; a group that needs all
+as soon as every position in it lies before the window of the request's next token (pages that hold one of the
+group's ``keep_first`` first positions excepted: those are read by every later token); a group that needs all
 keys holds its pages until the request ends.
 
 Policy, after the reference's BlockManager (engine/block_manager.cpp): pages are handed out least-recently-freed
@@ -47,6 +48,7 @@ class GroupConfig:
     num_pages: int
     window: int = 0          # 0 = all keys are kept; w > 0 = positions further back than w are given up
     units: tuple = ()        # cache unit ids served by this group (informational)
+    keep_first: int = 0      # with a window: positions 0..keep_first-1 are read for ever, their pages are never given up
 
 
 class PagePool:
@@ -308,7 +310,8 @@ class CacheManager:
                 continue
             table = lease.tables[g]
             upto = min(self._first_needed_page(g, computed), len(table))
-            for i in range(lease.first_held[g], upto):
+            kept_pages = self.num_pages_for(self.groups[g].keep_first)     # pages 0..kept_pages-1 hold a kept position
+            for i in range(max(lease.first_held[g], kept_pages), upto):
                 if table[i] >= 0:
                     self.pools[g].give_back(table[i])
                     table[i] = -1

@@ -27,6 +27,7 @@ def _library():
         lib.cvb_cm_create.restype = c_void_p
         lib.cvb_cm_create.argtypes = [c_int, POINTER(c_int), POINTER(c_int), c_int, c_int, c_int, c_int]
         lib.cvb_cm_destroy.argtypes = [c_void_p]
+        lib.cvb_cm_set_keep_first.argtypes = [c_void_p, c_int, c_int]
         for name in ("cvb_cm_tables", "cvb_cm_table_len"):
             getattr(lib, name).restype = POINTER(c_int)
             getattr(lib, name).argtypes = [c_void_p, c_int]
@@ -124,6 +125,9 @@ class NativeCacheManager:
                                                    1 if prefix_caching else 0))
         if not self._h:
             raise ValueError("the cache manager could not be created from these sizes")
+        for g, cfg in enumerate(self.groups):
+            if getattr(cfg, "keep_first", 0):
+                self._lib.cvb_cm_set_keep_first(self._h, g, int(cfg.keep_first))
 
         def view(ptr, shape):
             n = int(np.prod(shape))

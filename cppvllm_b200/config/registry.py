@@ -25,15 +25,18 @@ class Architecture:
     parse_config: Callable[[Mapping[str, Any]], Any]
     build_spec: Callable[[Any], Any]
     model_types: tuple = ()
+    builtin: bool = False        # one of the package's own architectures
+    default: bool = False        # takes a config.json that names no architecture (see resolve_architecture)
 
 
 _ARCHITECTURES: Dict[str, Architecture] = {}
 
 
-def register_architecture(name: str, parse_config, build_spec, model_types=(), replace: bool = False) -> Architecture:
+def register_architecture(name: str, parse_config, build_spec, model_types=(), replace: bool = False, builtin: bool = False,
+                          default: bool = False) -> Architecture:
     if name in _ARCHITECTURES and not replace:
         raise ValueError(f"architecture '{name}' is already registered")
-    arch = Architecture(name, parse_config, build_spec, tuple(model_types))
+    arch = Architecture(name, parse_config, build_spec, tuple(model_types), bool(builtin), bool(default))
     _ARCHITECTURES[name] = arch
     return arch
 
@@ -47,12 +50,16 @@ def registered_architectures():
 
 
 def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
-    """Choose the architecture for a config.json: ``architectures[0]``, else ``model_type``.
+    """Choose the architecture for a config.json: ``architectures[0]`` (or a string under ``architecture``), else
+    ``model_type``.
 
-    A config.json with neither key is accepted only while exactly one architecture is registered (the
-    reference never reads either key, so such files exist)."""
+    A config.json with neither key is accepted only while exactly one architecture is registered, or while none
+    but the package's own are and one of them is the default (the reference never reads either key, so such files
+    exist)."""
     from .. import models as _models  # noqa: F401  (the package's own architectures register themselves on import)
     archs = config_dict.get("architectures")
+    if not archs and isinstance(config_dict.get("architecture"), str):
+        archs = [config_dict["architecture"]]
     if isinstance(archs, (list, tuple)) and archs:
         name = str(archs[0])
         if name in _ARCHITECTURES:
@@ -68,5 +75,9 @@ def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
                           f"{registered_architectures()}")
     if len(_ARCHITECTURES) == 1:
         return next(iter(_ARCHITECTURES.values()))
+    if all(a.builtin for a in _ARCHITECTURES.values()):
+        for a in _ARCHITECTURES.values():
+            if a.default:
+                return a
     raise ConfigError("config.json names no architecture ('architectures' or 'model_type'); registered: "
                       f"{registered_architectures()}")

@@ -1,14 +1,18 @@
-// General paged attention: any head size, any number of heads and groups, float or bf16, optional window.
+// General paged attention: any head size, any number of heads and groups, float or bf16, optional window, optional kept
+// first positions, pages that hold keys and values or keys that are also the values.
 // One block per (query token, query head).  It serves prompt portions and decoded tokens alike, because
 // every query token is handled on its own: its keys are those of its request at positions lo..p, read
 // through the request's block table, where p is the token's absolute position and lo = 0 or, with a
-// window w > 0, max(0, p - w + 1).  The keys of the step's own tokens are already in the pages (the
-// projection kernel writes before this kernel reads).
+// window w > 0, max(0, p - w + 1).  With `keep_first` = f > 0 the positions 0..f-1 stay visible after the window has
+// passed them: the token then reads 0..min(f, lo)-1 and lo..p (two runs of tiles).  The keys of the step's own tokens
+// are already in the pages (the projection kernel writes before this kernel reads).  `planes` = 2: a page is
+// [K | V][kv head][slot][hd]; `planes` = 1: a page is [kv head][slot][hd] and a key is also its value.  Queries are
+// read from rows of `q_stride` elements (the packed output of a projection, or [T, H, hd] itself).
 //
 // Formulas (reference kernels/paged_attention.cu:89-359 and model/model_architecture.cpp:134,147):
 //   query head h uses kv head h / (H / KV);  s_j = scale * q . k_j  for lo <= j <= p, others excluded;
 //   running maximum m, sum l and accumulator in float with expf;  o = sum_j p_j v_j / l;  rounded to T.
-// Keys are walked in tiles of blockDim.x from lo, so the order of the float sums depends only on (lo, p):
+// Keys are walked in tiles of blockDim.x from the start of each run, so the order of the float sums depends only on (f, lo, p):
 // not on how the prompt was cut into steps, nor on the batch, nor on which pages hold the keys.
 #include "common.cuh"
 
@@ -22,8 +26,8 @@ __global__ void __launch_bounds__(kAttnThreads)
 paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ cache,
                                const int* __restrict__ block_tables, int table_width,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                               int H, int KV, int hd, int page_size, int window, float scale, int num_pages,
-                               int* __restrict__ err) {
+                               int H, int KV, int hd, int page_size, int window, int keep_first, int planes, int q_stride,
+                               float scale, int num_pages, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ int64_t smem64[];
@@ -41,7 +45,7 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
     const int lo = window > 0 ? max(0, p - window + 1) : 0;
     const int* table = block_tables + static_cast<int64_t>(seq) * table_width;
 
-    for (int e = tid; e < hd; e += kAttnThreads) qs[e] = to_float(q[(t * H + h) * hd + e]);
+    for (int e = tid; e < hd; e += kAttnThreads) qs[e] = to_float(q[t * q_stride + h * hd + e]);
     __syncthreads();
 
     float acc[kMaxDimsPerThread];
@@ -49,18 +53,21 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
     for (int i = 0; i < kMaxDimsPerThread; ++i) acc[i] = 0.f;
     float m = -INFINITY, l = 0.f;
 
-    for (int start = lo; start <= p; start += kAttnThreads) {
+    const int kept = min(keep_first, lo);               // positions 0..kept-1 lie before the window and stay visible
+    for (int run = kept > 0 ? 0 : 1; run < 2; ++run) {
+    const int first = run == 0 ? 0 : lo, last = run == 0 ? kept - 1 : p;
+    for (int start = first; start <= last; start += kAttnThreads) {
         const int j = start + tid;
         float s = -INFINITY;
         int64_t voff = -1;
-        if (j <= p) {
+        if (j <= last) {
             const int slot = j / page_size;
             int page = slot < table_width ? table[slot] : -1;
             if (page < 0 || page >= num_pages) {
                 atomicExch(err, 4);                     // a key this token must see has no page
             } else {
-                const int64_t koff = (((static_cast<int64_t>(page) * 2 + 0) * KV + kvh) * page_size + j % page_size) * hd;
-                voff = (((static_cast<int64_t>(page) * 2 + 1) * KV + kvh) * page_size + j % page_size) * hd;
+                const int64_t koff = (((static_cast<int64_t>(page) * planes + 0) * KV + kvh) * page_size + j % page_size) * hd;
+                voff = (((static_cast<int64_t>(page) * planes + (planes - 1)) * KV + kvh) * page_size + j % page_size) * hd;
                 const T* kp = cache + koff;
                 float d = 0.f;
                 for (int e = 0; e < hd; ++e) d = fmaf(qs[e], to_float(kp[e]), d);
@@ -75,7 +82,7 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
         const float tile_sum = block_sum(pj, scratch);  // also orders the writes above before the reads below
         const float corr = (m == -INFINITY) ? 0.f : expf(m - m_new);
         l = l * corr + tile_sum;
-        const int n = min(kAttnThreads, p - start + 1);
+        const int n = min(kAttnThreads, last - start + 1);
 #pragma unroll
         for (int i = 0; i < kMaxDimsPerThread; ++i) {
             const int d = tid + i * kAttnThreads;
@@ -91,6 +98,7 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
         m = m_new;
         __syncthreads();
     }
+    }
     const float inv_l = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < kMaxDimsPerThread; ++i) {
@@ -105,20 +113,21 @@ using namespace cvb;
 
 extern "C" int cvb_paged_attention_general(void* out, const void* q, const void* cache, const int* block_tables,
                                            int table_width, const int* seq_of_token, const int* positions, int T,
-                                           int H, int KV, int hd, int page_size, int window, float scale,
-                                           int num_pages, int dtype, int* err_flag, cudaStream_t stream) {
+                                           int H, int KV, int hd, int page_size, int window, int keep_first, int planes,
+                                           int q_stride, float scale, int num_pages, int dtype, int* err_flag,
+                                           cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || H <= 0 || KV <= 0 || hd <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0)
         return CVB_E_SIZE;
     if (hd > kAttnThreads * kMaxDimsPerThread) return CVB_E_SIZE;
-    if (H % KV) return CVB_E_SHAPE;
+    if (H % KV || (planes != 1 && planes != 2) || keep_first < 0 || q_stride < H * hd) return CVB_E_SHAPE;
     if (H > 65535) return CVB_E_SIZE;
     dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>(H));
     const size_t smem = kAttnThreads * sizeof(int64_t) + (static_cast<size_t>(hd) + kAttnThreads + 32) * sizeof(float);
 #define CALL(TY)                                                                                         \
     launch_kernel(paged_attention_general_kernel<TY>, dim3(grid), dim3(kAttnThreads), smem, stream,                             \
         (TY*)out, (const TY*)q, (const TY*)cache, block_tables, table_width, seq_of_token, positions, H, \
-        KV, hd, page_size, window, scale, num_pages, err_flag)
+        KV, hd, page_size, window, keep_first, planes, q_stride, scale, num_pages, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

@@ -37,6 +37,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemv_bf16": ["gemv_bf16.cu"],
     "gemm_bf16": ["gemm_tcgen05.cu"],
     "attn_tcgen05": ["attention_tcgen05.cu"],
+    "resid32": ["residual_f32.cu"],
+    "moe": ["moe.cu"],
     # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
 }

@@ -32,6 +32,7 @@ void* cvb_cm_create(int num_groups, const int* num_pages, const int* windows, in
     m->page_size = page_size; m->width = width; m->num_slots = num_slots; m->num_groups = num_groups;
     m->prefix_caching = prefix_caching != 0;
     m->window.assign(windows, windows + num_groups);
+    m->keep_first.assign(num_groups, 0);
     m->pools.resize(num_groups);
     m->tables.resize(num_groups); m->table_len.resize(num_groups); m->first_held.resize(num_groups);
     for (int g = 0; g < num_groups; ++g) {
@@ -46,6 +47,15 @@ void* cvb_cm_create(int num_groups, const int* num_pages, const int* windows, in
 }
 
 void cvb_cm_destroy(void* h) { delete M(h); }
+
+// A windowed group whose first `keep_first` positions are read by every later token: the pages that hold them are never
+// given back while the request lives.  Set right after creation.
+int cvb_cm_set_keep_first(void* h, int g, int keep_first) {
+    Manager* m = M(h);
+    if (g < 0 || g >= m->num_groups || keep_first < 0) return kErrMisuse;
+    m->keep_first[g] = keep_first;
+    return kOk;
+}
 
 // Arrays that the wrapper reads in place (they never move): a group's dense block tables and their lengths, and the
 // per-slot counters.
@@ -192,7 +202,10 @@ int cvb_cm_advance(void* h, int slot, int computed) {
         const int len = m->table_len[g][slot];
         int upto = m->first_needed(g, computed);
         if (upto > len) upto = len;
-        for (int i = m->first_held[g][slot]; i < upto; ++i)
+        const int kept_pages = m->pages_for(m->keep_first[g]);
+        int from = m->first_held[g][slot];
+        if (from < kept_pages) from = kept_pages;
+        for (int i = from; i < upto; ++i)
             if (tab[i] >= 0) {
                 m->pools[g].give_back(tab[i]);
                 tab[i] = -1;

@@ -33,6 +33,7 @@ DEVICE_ERRORS = {
     4: "attention needed a key whose page is missing from the block table",
     5: "a bounded wait in a kernel ran out",
     6: "a kernel found its shared memory misaligned for swizzled tiles",
+    7: "a routed feed-forward met an expert index outside its experts",
 }
 
 
@@ -206,6 +207,137 @@ def gather_rows(out: torch.Tensor, src: torch.Tensor, rows: torch.Tensor) -> tor
     return out
 
 
+# ---- a residual stream in float under activations of any element type ----------------------------------------
+
+_resid32 = None
+
+
+def _resid32_lib():
+    global _resid32
+    if _resid32 is None:
+        lib = load_library("resid32")
+        for name in ("cvb_embed_positions", "cvb_resid_update", "cvb_gelu_tanh", "cvb_write_rows"):
+            getattr(lib, name).restype = c_int
+        _resid32 = lib
+    return _resid32
+
+
+def embed_positions(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor, positions: torch.Tensor, scale: float = 1.0,
+                    pos_table: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[t] = float(table[tokens[t]]) * scale + float(pos_table[positions[t]]); `out2` receives a second copy."""
+    _cuda(out, table, tokens, positions, pos_table, out2); _contig(out, table, tokens, positions, pos_table, out2)
+    T, D = out.shape
+    if (out.dtype != torch.float32 or tokens.dtype != torch.int32 or positions.dtype != torch.int32 or tokens.numel() < T
+            or positions.numel() < T or table.shape[1] != D
+            or (pos_table is not None and (pos_table.dtype != table.dtype or pos_table.shape[1] != D))
+            or (out2 is not None and (out2.dtype != torch.float32 or out2.shape != out.shape))):
+        raise KernelError("embed_positions: out float32 [T, D]; tokens, positions int32 [T]; table [V, D] and pos_table [P, D] of "
+                          "one element type")
+    _check(_resid32_lib().cvb_embed_positions(
+        _ptr(out), _ptr(out2), _ptr(table), _ptr(pos_table), _ptr(tokens), _ptr(positions), c_int(T), c_int(D),
+        c_int(table.shape[0]), c_int(pos_table.shape[0] if pos_table is not None else 0), c_float(scale),
+        c_int(dtype_code(table.dtype)), _ptr(error_flag(out.device)), _stream()), "embed_positions")
+    return out
+
+
+def resid_update(h: torch.Tensor, deltas=(), rows: Optional[torch.Tensor] = None, vector: Optional[torch.Tensor] = None,
+                 norm_weight: Optional[torch.Tensor] = None, eps: float = 0.0, out: Optional[torch.Tensor] = None):
+    """h (float32 [T, D], in place) <- ((h + (deltas[0] + deltas[1])) + rows) + vector, each addend optional: up to two
+    deltas of the activations' element type [T, D], float32 rows [T, D], a float32 vector [D].  With `norm_weight`
+    (float32 [D]) also out <- RMSNorm(h) * norm_weight, rounded once, in out's element type.  Returns out (or h)."""
+    deltas = tuple(d for d in deltas if d is not None)
+    if len(deltas) > 2:
+        raise KernelError("resid_update: at most two deltas")
+    d1 = deltas[0] if deltas else None
+    d2 = deltas[1] if len(deltas) > 1 else None
+    _cuda(h, d1, d2, rows, vector, norm_weight, out); _contig(h, d1, d2, rows, vector, norm_weight, out)
+    T, D = h.shape
+    act = out.dtype if out is not None else (d1.dtype if d1 is not None else torch.float32)
+    if h.dtype != torch.float32:
+        raise KernelError("resid_update: the residual stream must be float32")
+    for d in deltas:
+        if d.shape != h.shape or d.dtype != act:
+            raise KernelError("resid_update: deltas must be shaped like h and share the output's element type")
+    if rows is not None and (rows.dtype != torch.float32 or rows.shape != h.shape):
+        raise KernelError("resid_update: rows must be float32, shaped like h")
+    if vector is not None and (vector.dtype != torch.float32 or vector.numel() != D):
+        raise KernelError("resid_update: vector must be float32 [D]")
+    if norm_weight is not None and (out is None or norm_weight.dtype != torch.float32 or norm_weight.numel() != D
+                                    or out.shape != h.shape):
+        raise KernelError("resid_update: the norm needs a float32 weight [D] and an out shaped like h")
+    _check(_resid32_lib().cvb_resid_update(_ptr(h), _ptr(d1), _ptr(d2), _ptr(rows), _ptr(vector), _ptr(norm_weight), _ptr(out),
+                                           c_int(T), c_int(D), c_float(eps), c_int(dtype_code(act)), _stream()), "resid_update")
+    return out if out is not None else h
+
+
+def gelu_tanh(out: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    _cuda(out, x); _contig(out, x)
+    if out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("gelu_tanh: out must match x")
+    _check(_resid32_lib().cvb_gelu_tanh(_ptr(out), _ptr(x), c_int64(x.numel()), c_int(dtype_code(x.dtype)), _stream()), "gelu_tanh")
+    return out
+
+
+def write_rows(pages: torch.Tensor, src: torch.Tensor, slots: torch.Tensor, col0: int, heads: int, width: int,
+               page_size: int) -> torch.Tensor:
+    """pages[slot // page_size, head, slot % page_size, :] = src[t, col0 + head * width : ...] for every row t of src."""
+    _cuda(pages, src, slots); _contig(pages, src, slots)
+    T = src.shape[0]
+    if pages.dtype != src.dtype or slots.dtype != torch.int32 or slots.numel() < T or src.dim() != 2:
+        raise KernelError("write_rows: pages and src of one element type, slots int32 [T]")
+    _check(_resid32_lib().cvb_write_rows(_ptr(pages), _ptr(src), _ptr(slots), c_int(T), c_int(src.shape[1]), c_int(col0),
+                                         c_int(heads), c_int(width), c_int(page_size), c_int64(pages.numel()),
+                                         c_int(dtype_code(src.dtype)), _ptr(error_flag(src.device)), _stream()), "write_rows")
+    return pages
+
+
+# ---- routed feed-forward ---------------------------------------------------------------------------------------
+
+_moe = None
+
+
+def _moe_lib():
+    global _moe
+    if _moe is None:
+        lib = load_library("moe")
+        for name in ("cvb_route_topk", "cvb_expert_rows"):
+            getattr(lib, name).restype = c_int
+        _moe = lib
+    return _moe
+
+
+def route_topk(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router: torch.Tensor,
+               bias: Optional[torch.Tensor]) -> None:
+    """ids, weights [T, top]: the `top` largest of x @ router^T + bias (float32 arithmetic) and the softmax over them."""
+    _cuda(ids, weights, x, router, bias); _contig(ids, weights, x, router, bias)
+    T, D = x.shape
+    E = router.shape[0]
+    top = ids.shape[1]
+    if (ids.dtype != torch.int32 or weights.dtype != torch.float32 or router.dtype != torch.float32 or router.shape[1] != D
+            or ids.shape != (T, top) or weights.shape != (T, top) or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != E))):
+        raise KernelError("route_topk: ids int32 and weights float32 [T, top]; router float32 [E, D]; bias float32 [E]")
+    _check(_moe_lib().cvb_route_topk(_ptr(ids), _ptr(weights), _ptr(x), _ptr(router), _ptr(bias), c_int(T), c_int(D), c_int(E),
+                                     c_int(top), c_int(dtype_code(x.dtype)), _stream()), "route_topk")
+
+
+def expert_rows(y: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
+                w_down: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum_k weights[t, k] * down_e(silu(gate_e x) * up_e x), e = ids[t, k]; w_gate_up [E, 2 ff, D], w_down [E, D, ff]."""
+    _cuda(y, x, ids, weights, w_gate_up, w_down); _contig(y, x, ids, weights, w_gate_up, w_down)
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    if (y.shape != x.shape or y.dtype != x.dtype or w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype
+            or w_gate_up.shape != (E, 2 * F, D) or w_down.shape != (E, D, F) or ids.dtype != torch.int32
+            or weights.dtype != torch.float32 or ids.shape != weights.shape or ids.shape[0] != T):
+        raise KernelError("expert_rows: x, y [T, D], w_gate_up [E, 2 ff, D] and w_down [E, D, ff] of one element type; ids int32 and "
+                          "weights float32 [T, top]")
+    _check(_moe_lib().cvb_expert_rows(_ptr(y), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), c_int(T), c_int(D),
+                                      c_int(F), c_int(E), c_int(ids.shape[1]), c_int(dtype_code(x.dtype)),
+                                      _ptr(error_flag(x.device)), _stream()), "expert_rows")
+    return y
+
+
 # ---- projection epilogue: per-head norm, rotary, cache write --------------------------------------------------
 
 def qk_norm_rope_kv(q_out: torch.Tensor, qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
@@ -251,7 +383,11 @@ def qk_norm_rope_kv(q_out: torch.Tensor, qkv: torch.Tensor, q_weight: Optional[t
 def paged_attention_general(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                             seq_of_token: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
                             head_dim: int, page_size: int, scale: float, window: int = 0,
-                            num_tokens: Optional[int] = None) -> torch.Tensor:
+                            num_tokens: Optional[int] = None, keep_first: int = 0, keys_are_values: bool = False) -> torch.Tensor:
+    """One block per (token, query head); any head size.  `keep_first`: positions 0..keep_first-1 stay visible behind the
+    window.  `keys_are_values`: pages are [kv head, slot, head_dim] and a key is also its value (else [K|V, kv head, slot,
+    head_dim]).  `q` may be the packed output of a projection: rows of q.shape[1] elements whose first H * head_dim are
+    the queries."""
     _cuda(out, q, cache, block_tables, seq_of_token, positions)
     _contig(out, q, cache, block_tables, seq_of_token, positions)
     T = q.shape[0] if num_tokens is None else num_tokens
@@ -263,12 +399,15 @@ def paged_attention_general(out: torch.Tensor, q: torch.Tensor, cache: torch.Ten
         raise KernelError("paged_attention: seq_of_token and positions must be int32")
     if num_heads % num_kv_heads:
         raise KernelError(f"paged_attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
-    page_elems = 2 * num_kv_heads * page_size * head_dim
+    planes = 1 if keys_are_values else 2
+    page_elems = planes * num_kv_heads * page_size * head_dim
     num_pages = cache.numel() // page_elems
+    q_stride = q.shape[1] if q.dim() == 2 else num_heads * head_dim
     _check(core().cvb_paged_attention_general(
         _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_of_token),
         _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
-        c_int(window), c_float(scale), c_int(num_pages), c_int(dtype_code(q.dtype)),
+        c_int(window), c_int(keep_first), c_int(planes), c_int(q_stride), c_float(scale), c_int(num_pages),
+        c_int(dtype_code(q.dtype)),
         _ptr(error_flag(q.device)), _stream()), "paged_attention_general")
     return out
 

@@ -108,6 +108,7 @@ struct Manager {
     bool prefix_caching = false;
     long long prefix_hits = 0;
     std::vector<int> window;
+    std::vector<int> keep_first;              // per group: positions 0..keep_first-1 stay readable behind the window
     std::vector<Pool> pools;
     std::vector<std::vector<int>> tables;     // per group [num_slots][width], -1 where nothing is held
     std::vector<std::vector<int>> table_len;  // per group [num_slots]

@@ -83,7 +83,8 @@ class ModelRunner:
         spec = self.arch.build_spec(self.config)
         self.max_model_len = int(min(max_model_len, spec.max_positions) if spec.max_positions else max_model_len)
         self.workspace = Workspace(self.device, self.max_step_tokens, self.max_seqs)
-        self.rt = Runtime(self.device, dtype, self.workspace, plain_kernels=bool(use_ref_kernels))
+        stream_dtype = {None: None, "float32": torch.float32}[spec.residual_dtype]
+        self.rt = Runtime(self.device, dtype, self.workspace, plain_kernels=bool(use_ref_kernels), residual_dtype=stream_dtype)
         self.model = CausalLM(spec, self.rt)
         self.model.bind(load_weights(self.model, model_dir, self.device, dtype))
         self.vocab_size = self.model.vocab_size
@@ -118,7 +119,7 @@ class ModelRunner:
             print("[cppvllm_b200] the prefix cache is off: it needs one group of cache units that keeps all keys and "
                   "no per-request state", file=sys.stderr, flush=True)
             enable_prefix_caching = False
-        groups = [GroupConfig(self.num_pages, cs.window, tuple(m)) for cs, m in self.group_specs]
+        groups = [GroupConfig(self.num_pages, cs.window, tuple(m), keep_first=cs.keep_first) for cs, m in self.group_specs]
         if native_cache_manager and groups:
             # the C++ manager keeps the block tables as dense arrays that the steps read in place
             self.cache = NativeCacheManager(groups, page_size, n_slots, self.table_width, prefix_caching=enable_prefix_caching)

@@ -44,4 +44,5 @@ def build_qwen3_spec(cfg: Qwen3Config) -> ModelSpec:
     )
 
 
-register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, build_qwen3_spec, model_types=("qwen3",), replace=True)
+register_architecture("Qwen3ForCausalLM", Qwen3Config.from_dict, build_qwen3_spec, model_types=("qwen3",), replace=True,
+                      builtin=True, default=True)

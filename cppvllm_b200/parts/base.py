@@ -2,7 +2,8 @@
 
 Categories: ``mixer`` (token mixing: attention here), ``ffn`` (feed-forward), ``norm``, ``position``
 (position encoding), ``block`` (arrangement of mixer, feed-forward and norms with the residual stream),
-``embedding`` and ``head``.  A part
+``embedding``, ``head`` and ``input`` (something added to the residual stream in front of a run entry, for instance
+what a repeated pass over some layers receives).  A part
 
 * is constructed as ``cls(runtime, prefix=..., names=..., **params)``: all sizes and constants arrive as
   parameters; a part never looks at a model configuration and does not know which model it is in;
@@ -23,7 +24,7 @@ import torch
 # ---- registry ------------------------------------------------------------------------------------------
 
 _REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in
-                                         ("mixer", "ffn", "norm", "position", "block", "embedding", "head")}
+                                         ("mixer", "ffn", "norm", "position", "block", "embedding", "head", "input")}
 
 
 def register_part(category: str, kind: str, cls: type = None, replace: bool = False):
@@ -75,14 +76,20 @@ class CacheSpec:
     with the page's positions inserted at `token_axis`.  Units with equal specs form one group of pages; the cache
     manager hands out pages and block tables and never looks inside a page.
       attention:   CacheSpec.keys_and_values(kv_heads, head_dim)   pages [2, kv_heads, page, head_dim]
-      a latent:    CacheSpec((width,), token_axis=0)                pages [page, width]"""
+      a latent:    CacheSpec((width,), token_axis=0)                pages [page, width]
+      keys only:   CacheSpec.keys_only(kv_heads, head_dim)          pages [kv_heads, page, head_dim]"""
     entry_shape: Tuple[int, ...]
     token_axis: int = 0
     window: int = 0           # 0 = all positions; w > 0 = only the last w positions are ever read (older pages go back)
+    keep_first: int = 0       # with a window: the first positions 0..keep_first-1 are read for ever (their pages stay)
 
     @staticmethod
     def keys_and_values(num_kv_heads: int, head_dim: int, window: int = 0) -> "CacheSpec":
         return CacheSpec((2, int(num_kv_heads), int(head_dim)), token_axis=2, window=int(window))
+
+    @staticmethod
+    def keys_only(num_kv_heads: int, head_dim: int, window: int = 0, keep_first: int = 0) -> "CacheSpec":
+        return CacheSpec((int(num_kv_heads), int(head_dim)), token_axis=1, window=int(window), keep_first=int(keep_first))
 
     def page_shape(self, page_size: int) -> Tuple[int, ...]:
         return tuple(self.entry_shape[:self.token_axis]) + (page_size,) + tuple(self.entry_shape[self.token_axis:])
@@ -160,6 +167,11 @@ class Runtime:
     dtype: torch.dtype
     workspace: Workspace
     plain_kernels: bool = False
+    residual_dtype: Optional[torch.dtype] = None      # element type of the residual stream; None = the activations' type
+
+    @property
+    def stream_dtype(self) -> torch.dtype:
+        return self.residual_dtype if self.residual_dtype is not None else self.dtype
 
 
 class Part:
@@ -222,6 +234,16 @@ class FeedForward(Part):
     category = "ffn"
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class StreamInput(Part):
+    """Adds to the residual stream in front of a run entry."""
+    category = "input"
+
+    def forward(self, h, pending, embedded, index: int):
+        """h: residual stream; pending: deltas not yet added (a tensor, a tuple of tensors or None); embedded: the
+        embedding's output of this step; index: which occurrence this is.  Returns (h, pending)."""
         raise NotImplementedError
 
 

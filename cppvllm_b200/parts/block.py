@@ -17,6 +17,8 @@ from .base import Block, build_part, register_part
 class PreNormBlock(Block):
     def __init__(self, runtime, prefix="", names=None, *, mixer, ffn, mixer_norm, ffn_norm):
         super().__init__(runtime, prefix, names)
+        if ffn is None or ffn_norm is None:
+            raise ValueError("a pre-norm block needs a feed-forward and a norm in front of it")
         self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
 
     def parts(self):

@@ -34,12 +34,13 @@ class CausalLM:
                     raise ValueError(f"mixer names position encoding '{pos_name}', which the spec does not define")
                 mixer_extra["position"] = self.positions[pos_name]
             mixer = mixer_cls(runtime, prefix=ls.mixer.prefix, names=dict(ls.mixer.names), **mparams, **mixer_extra)
-            ffn = build_part("ffn", ls.ffn, runtime)
+            ffn = build_part("ffn", ls.ffn, runtime) if ls.ffn is not None else None
             mixer_norm = build_part("norm", ls.mixer_norm, runtime)
-            ffn_norm = build_part("norm", ls.ffn_norm, runtime)
+            ffn_norm = build_part("norm", ls.ffn_norm, runtime) if ls.ffn_norm is not None else None
             block_cls = part_class("block", ls.block)
             self.blocks.append(block_cls(runtime, mixer=mixer, ffn=ffn, mixer_norm=mixer_norm, ffn_norm=ffn_norm,
                                          **ls.block_params))
+        self.inputs = {name: build_part("input", ps, runtime) for name, ps in spec.inputs.items()}
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.lm_head, runtime)
         self.run_order: List[RunEntry] = spec.resolved_run_order()
@@ -81,6 +82,7 @@ class CausalLM:
         yield self.final_norm
         yield self.head
         yield from self.positions.values()
+        yield from self.inputs.values()
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         specs: Dict[str, WeightSpec] = {}
@@ -107,13 +109,21 @@ class CausalLM:
         total = 0
         for e in self.run_order:
             total += sum(p.weight_bytes() for p in self.blocks[e.layer].parts())
+            if e.input is not None:
+                total += self.inputs[e.input].weight_bytes()
         return total + self.final_norm.weight_bytes() + self.head.weight_bytes()
 
     # ---- step ----------------------------------------------------------------------------------------
     def forward_hidden(self, ctx, caches, states):
-        h = self.embedding.forward(ctx.tokens, ctx.num_tokens)
+        positioned = getattr(self.embedding, "forward_step", None)     # an embedding that also reads the positions
+        if positioned is not None:
+            h, embedded = positioned(ctx, keep=bool(self.inputs))
+        else:
+            h = embedded = self.embedding.forward(ctx.tokens, ctx.num_tokens)
         pending = None
         for i, e in enumerate(self.run_order):
+            if e.input is not None:
+                h, pending = self.inputs[e.input].forward(h, pending, embedded, e.input_index)
             h, pending = self.blocks[e.layer].forward(h, pending, ctx, caches.get(i), states.get(i))
         return h, pending
 
@@ -122,9 +132,13 @@ class CausalLM:
         R = ctx.num_logit_rows
         ws = self.rt.workspace
         rows_h = ops.gather_rows(ws.rows("head_rows", R, self.hidden_size, h.dtype), h, ctx.logit_rows)
-        normed = ws.rows("head_normed", R, self.hidden_size, h.dtype)
-        if pending is not None:
-            rows_p = ops.gather_rows(ws.rows("head_pending", R, self.hidden_size, h.dtype), pending, ctx.logit_rows)
+        normed = ws.rows("head_normed", R, self.hidden_size, self.rt.dtype)
+        if isinstance(pending, tuple):               # several deltas (a block whose sublayers run side by side)
+            rows_p = tuple(ops.gather_rows(ws.rows(f"head_pending{i}", R, self.hidden_size, p.dtype), p, ctx.logit_rows)
+                           for i, p in enumerate(pending))
+            self.final_norm.add_forward(rows_h, rows_p, out=normed)
+        elif pending is not None:
+            rows_p = ops.gather_rows(ws.rows("head_pending", R, self.hidden_size, pending.dtype), pending, ctx.logit_rows)
             self.final_norm.add_forward(rows_h, rows_p, out=normed)
         else:
             self.final_norm.forward(rows_h, out=normed)

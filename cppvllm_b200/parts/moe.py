@@ -1,0 +1,97 @@
+"""Feed-forward parts beside the gated dense one (parts/mlp.py):
+
+* ``act_mlp``: y = Wdown act(Wup x), no gate, no biases; act = "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).
+* ``routed_glu``: a mixture of experts.  Router logits z = Wr x + b in float32 (x as the norm rounded it); each token uses
+  the ``top`` experts with the largest logits, weighted by the softmax over the chosen logits only; an expert is
+  Wdown (silu(Wgate x) * (Wup x)) without biases; the output is the weighted sum of the chosen experts' outputs.  Expert e's
+  tensors are ``<prefix>e<e>.gate|up|down``; they are stacked at load time into [E, 2 ff, D] (gate rows over up rows) and
+  [E, D, ff], so that a kernel reaches every expert from one base address.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, WeightSpec, register_part
+
+
+@register_part("ffn", "act_mlp")
+class ActMLP(FeedForward):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh",
+                 up_name: str = "up", down_name: str = "down"):
+        super().__init__(runtime, prefix, names)
+        if activation != "gelu_tanh":
+            raise ValueError(f"activation '{activation}' is not built; built: gelu_tanh")
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.up_name, self.down_name = up_name, down_name
+        self.w_up = self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, I = self.hidden_size, self.intermediate_size
+        return {self.full_name(self.up_name): WeightSpec((I, D)), self.full_name(self.down_name): WeightSpec((D, I))}
+
+    def bind(self, tensors) -> None:
+        self.w_up, self.w_down = tensors[self.full_name(self.up_name)], tensors[self.full_name(self.down_name)]
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
+
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        ws = self.rt.workspace
+        up = self._project(x, self.w_up, ws.rows("ffn_up", T, self.intermediate_size, x.dtype), T)
+        ops.gelu_tanh(up, up)
+        return self._project(up, self.w_down, ws.rows("ffn_out", T, self.hidden_size, x.dtype), T)
+
+
+@register_part("ffn", "routed_glu")
+class RoutedGLU(FeedForward):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int, num_experts: int, top: int,
+                 router_name: str = "router", router_bias_name: str = "router.b", expert_prefix: str = "e"):
+        super().__init__(runtime, prefix, names)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.num_experts, self.top = int(num_experts), int(top)
+        if not (0 < self.top <= self.num_experts):
+            raise ValueError(f"a token cannot use {self.top} of {self.num_experts} experts")
+        self.router_name, self.router_bias_name, self.expert_prefix = router_name, router_bias_name, expert_prefix
+        self.w_router = self.b_router = self.w_gate_up = self.w_down = None
+
+    def _expert(self, e: int, which: str) -> str:
+        return self.full_name(f"{self.expert_prefix}{e}.{which}")
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, I, E = self.hidden_size, self.intermediate_size, self.num_experts
+        specs = {self.full_name(self.router_name): WeightSpec((E, D), role="vector"),
+                 self.full_name(self.router_bias_name): WeightSpec((E,), role="vector")}
+        for e in range(E):
+            specs[self._expert(e, "gate")] = WeightSpec((I, D))
+            specs[self._expert(e, "up")] = WeightSpec((I, D))
+            specs[self._expert(e, "down")] = WeightSpec((D, I))
+        return specs
+
+    def bind(self, tensors) -> None:
+        E = self.num_experts
+        self.w_router = tensors[self.full_name(self.router_name)]
+        self.b_router = tensors[self.full_name(self.router_bias_name)]
+        gu = [torch.cat([tensors[self._expert(e, "gate")], tensors[self._expert(e, "up")]], dim=0) for e in range(E)]
+        self.w_gate_up = torch.stack(gu, dim=0).to(self.rt.dtype).contiguous()
+        self.w_down = torch.stack([tensors[self._expert(e, "down")] for e in range(E)], dim=0).to(self.rt.dtype).contiguous()
+
+    def weight_bytes(self) -> int:
+        """What a decoded token reads: the router and `top` of the experts."""
+        per_expert = (self.w_gate_up.numel() + self.w_down.numel()) * self.w_down.element_size() // self.num_experts
+        return self.w_router.numel() * 4 + self.b_router.numel() * 4 + self.top * per_expert
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        ws = self.rt.workspace
+        ids = ws.rows("moe_ids", T, self.top, torch.int32)
+        weights = ws.rows("moe_weights", T, self.top, torch.float32)
+        ops.route_topk(ids, weights, x, self.w_router, self.b_router)
+        y = ws.rows("ffn_out", T, self.hidden_size, x.dtype)
+        return ops.expert_rows(y, x, ids, weights, self.w_gate_up, self.w_down)

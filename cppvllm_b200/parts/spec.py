@@ -10,11 +10,15 @@ tensor-name prefixes.
   full tensor names (a tied output head names the embedding's table).
 * ``LayerSpec``: the parts of one layer and the name of their arrangement (``block``).  Layers need not be
   alike: each has its own mixer and feed-forward spec.
-* ``RunEntry(layer, cache, writes_cache)``: one item of the run list.  ``layer`` indexes ``layers`` and may
+* ``RunEntry(layer, cache, writes_cache, input, input_index)``: one item of the run list.  ``layer`` indexes ``layers`` and may
   occur several times (weights shared between runs).  ``cache`` is the id of the cache unit the mixer uses in
   this run; two entries with the same id share keys and values, and the entry with ``writes_cache=False``
   only reads what the other wrote (a layer that reads another layer's cache).  ``None`` means one unit per
   entry, written by it.  Per-request state of fixed size, if the mixer declares any, belongs to the entry.
+  ``input`` names one of the spec's ``inputs`` (parts that add to the residual stream in front of the entry: what a
+  repeated pass over some layers receives, for instance); ``input_index`` says which occurrence this is.
+* ``residual_dtype``: ``"float32"`` keeps the residual stream in 32-bit under activations of any element type (the
+  embedding, the norms and the blocks of such a model are the kinds that work on a 32-bit stream).
 """
 from __future__ import annotations
 
@@ -33,9 +37,9 @@ class PartSpec:
 @dataclass
 class LayerSpec:
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: Optional[PartSpec]                 # None: the layer has no feed-forward (blocks that allow it)
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: Optional[PartSpec] = None     # None: the arrangement has one norm only
     block: str = "prenorm"
     block_params: Dict[str, Any] = field(default_factory=dict)
 
@@ -45,6 +49,8 @@ class RunEntry:
     layer: int
     cache: Optional[int] = None
     writes_cache: bool = True
+    input: Optional[str] = None
+    input_index: int = 0
 
 
 @dataclass
@@ -61,6 +67,8 @@ class ModelSpec:
     max_positions: int = 0
     eos_token_ids: tuple = ()
     init: Dict[str, float] = field(default_factory=dict)            # defaults for random weights
+    inputs: Dict[str, PartSpec] = field(default_factory=dict)       # parts that add to the stream in front of run entries
+    residual_dtype: Optional[str] = None                            # "float32": a 32-bit residual stream
 
     def resolved_run_order(self) -> List[RunEntry]:
         order = self.run_order if self.run_order is not None else [RunEntry(i) for i in range(len(self.layers))]
@@ -73,7 +81,9 @@ class ModelSpec:
             if c is None:
                 c = next_free
                 next_free += 1
-            out.append(RunEntry(e.layer, c, e.writes_cache))
+            if e.input is not None and e.input not in self.inputs:
+                raise ValueError(f"run entry for layer {e.layer} names input '{e.input}', which the spec does not define")
+            out.append(RunEntry(e.layer, c, e.writes_cache, e.input, e.input_index))
         written = set()
         for e in out:
             if e.writes_cache:

@@ -77,7 +77,7 @@ def test_registry_resolves_by_name_then_model_type():
             register_architecture("ToyArch", None, None)
     finally:
         unregister_architecture("ToyArch")
-    assert resolve_architecture({}).name == "Qwen3ForCausalLM"     # the only one registered
+    assert resolve_architecture({}).name == "Qwen3ForCausalLM"     # the package's default
 
 
 def test_spec_is_data_with_sizes_from_config():
