@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_bf16": ["gemm_tcgen05.cu"],
     "attn_tcgen05": ["attention_tcgen05.cu"],
     "resid32": ["residual_f32.cu"],
+    "attn_keys": ["attention_keys.cu"],
     "moe": ["moe.cu"],
     # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],

@@ -29,7 +29,7 @@ _ERRORS = {
 DEVICE_ERRORS = {
     1: "a token id lies outside the embedding table",
     2: "a cache slot lies outside the page pool",
-    3: "a position lies outside the rotary tables (beyond max_position_embeddings)",
+    3: "a position lies outside the position tables (beyond the model's maximum position)",
     4: "attention needed a key whose page is missing from the block table",
     5: "a bounded wait in a kernel ran out",
     6: "a kernel found its shared memory misaligned for swizzled tiles",
@@ -291,6 +291,53 @@ def write_rows(pages: torch.Tensor, src: torch.Tensor, slots: torch.Tensor, col0
     return pages
 
 
+# ---- attention over keys that are also the values ------------------------------------------------------------------
+
+_attn_keys = None
+
+
+def _attn_keys_lib():
+    global _attn_keys
+    if _attn_keys is None:
+        lib = load_library("attn_keys")
+        lib.cvb_attn_keys_bf16.restype = c_int
+        lib.cvb_attn_keys_supported.restype = c_int
+        _attn_keys = lib
+    return _attn_keys
+
+
+def attn_keys_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int, q_stride: int) -> bool:
+    """The tensor-core kernel covers bf16, head sizes 16 to 128 in steps of 16, up to 64 query heads per kv head, and query
+    rows that start on 16-byte boundaries."""
+    return (dtype == torch.bfloat16 and q_stride % 8 == 0 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+            and num_kv_heads > 0 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 64)
+
+
+def attn_keys_tiles(q_lens, num_heads: int, num_kv_heads: int) -> int:
+    """Blocks per kv head: per request ceil(tokens / (64 // group))."""
+    tpt = 64 // (num_heads // num_kv_heads)
+    return sum((n + tpt - 1) // tpt for n in q_lens)
+
+
+def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
+                   positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                   page_size: int, scale: float, window: int = 0, keep_first: int = 0) -> torch.Tensor:
+    """Attention of prompt portions and decoded tokens over pages [kv head, slot, head_dim] whose keys are also the
+    values; `q` may be the packed output of a projection (rows of q.shape[1] elements, queries first)."""
+    _cuda(out, q, pages, block_tables, cu_seqlens, positions); _contig(out, q, pages, block_tables, cu_seqlens, positions)
+    if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_keys_bf16 takes bf16 queries, pages and output")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or cu_seqlens.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("attn_keys_bf16: block_tables [S, W], cu_seqlens and positions must be int32")
+    num_pages = pages.numel() // (num_kv_heads * page_size * head_dim)
+    _check(_attn_keys_lib().cvb_attn_keys_bf16(
+        _ptr(out), _ptr(q), c_int(q.shape[1]), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
+        _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), c_int(num_pages), _ptr(error_flag(q.device)),
+        _stream()), "attn_keys_bf16")
+    return out
+
+
 # ---- routed feed-forward ---------------------------------------------------------------------------------------
 
 _moe = None
@@ -300,7 +347,7 @@ def _moe_lib():
     global _moe
     if _moe is None:
         lib = load_library("moe")
-        for name in ("cvb_route_topk", "cvb_expert_rows"):
+        for name in ("cvb_route_topk", "cvb_expert_rows", "cvb_experts_grouped_bf16"):
             getattr(lib, name).restype = c_int
         _moe = lib
     return _moe
@@ -320,22 +367,85 @@ def route_topk(ids: torch.Tensor, weights: torch.Tensor, x: torch.Tensor, router
                                      c_int(top), c_int(dtype_code(x.dtype)), _stream()), "route_topk")
 
 
-def expert_rows(y: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, w_gate_up: torch.Tensor,
-                w_down: torch.Tensor) -> torch.Tensor:
-    """y[t] = sum_k weights[t, k] * down_e(silu(gate_e x) * up_e x), e = ids[t, k]; w_gate_up [E, 2 ff, D], w_down [E, D, ff]."""
-    _cuda(y, x, ids, weights, w_gate_up, w_down); _contig(y, x, ids, weights, w_gate_up, w_down)
+def expert_rows(y: torch.Tensor, hid: torch.Tensor, x: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+    """y[t] = sum_k weights[t, k] * down_e(silu(gate_e x) * up_e x), e = ids[t, k]; w_gate_up [E, 2 ff, D], w_down [E, D, ff];
+    `hid` [T * top, ff] is scratch.  Two kernels that read only the chosen experts' weights: for a few tokens, and for
+    float32."""
+    _cuda(y, hid, x, ids, weights, w_gate_up, w_down); _contig(y, hid, x, ids, weights, w_gate_up, w_down)
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
     F = F2 // 2
-    if (y.shape != x.shape or y.dtype != x.dtype or w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype
-            or w_gate_up.shape != (E, 2 * F, D) or w_down.shape != (E, D, F) or ids.dtype != torch.int32
+    top = ids.shape[1]
+    if (y.shape != x.shape or y.dtype != x.dtype or w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype or hid.dtype != x.dtype
+            or w_gate_up.shape != (E, 2 * F, D) or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or hid.numel() < T * top * F
             or weights.dtype != torch.float32 or ids.shape != weights.shape or ids.shape[0] != T):
-        raise KernelError("expert_rows: x, y [T, D], w_gate_up [E, 2 ff, D] and w_down [E, D, ff] of one element type; ids int32 and "
-                          "weights float32 [T, top]")
-    _check(_moe_lib().cvb_expert_rows(_ptr(y), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), c_int(T), c_int(D),
-                                      c_int(F), c_int(E), c_int(ids.shape[1]), c_int(dtype_code(x.dtype)),
-                                      _ptr(error_flag(x.device)), _stream()), "expert_rows")
+        raise KernelError("expert_rows: x, y [T, D], hid [T * top, ff], w_gate_up [E, 2 ff, D] and w_down [E, D, ff] of one element "
+                          "type; ids int32 and weights float32 [T, top]")
+    _check(_moe_lib().cvb_expert_rows(_ptr(y), _ptr(hid), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), c_int(T),
+                                      c_int(D), c_int(F), c_int(E), c_int(top), c_int(dtype_code(x.dtype)),
+                                      _ptr(error_flag(x.device)), _stream()), "expert_rows", kernels=2)
     return y
+
+
+def experts_grouped_supported(x_dtype: torch.dtype, D: int, F: int) -> bool:
+    """The grouped tensor-core products take bf16 and sizes that are multiples of 8."""
+    return x_dtype == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
+
+
+def experts_grouped_bf16(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows) -> torch.Tensor:
+    """The same result for many tokens: pairs sorted by expert on the device, two grouped products on the tensor cores, and
+    the weighted sum.  Scratch: offsets int32 [E + 1], sorted_pairs and slot_of int32 [T * top], hid bf16 [T * top, ff],
+    rows bf16 [T * top, D]."""
+    _cuda(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows)
+    _contig(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows)
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F = F2 // 2
+    top = ids.shape[1]
+    bf = torch.bfloat16
+    if (any(t.dtype != bf for t in (y, x, w_gate_up, w_down, hid, rows)) or y.shape != x.shape or w_gate_up.shape != (E, 2 * F, D)
+            or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or weights.dtype != torch.float32 or ids.shape != weights.shape
+            or ids.shape[0] != T or any(t.dtype != torch.int32 for t in (offsets, sorted_pairs, slot_of)) or offsets.numel() < E + 1
+            or sorted_pairs.numel() < T * top or slot_of.numel() < T * top or hid.numel() < T * top * F or rows.numel() < T * top * D):
+        raise KernelError("experts_grouped_bf16: bf16 x, y, weights and scratch of the documented sizes; int32 index scratch")
+    _check(_moe_lib().cvb_experts_grouped_bf16(
+        _ptr(y), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), _ptr(offsets), _ptr(sorted_pairs), _ptr(slot_of),
+        _ptr(hid), _ptr(rows), c_int(T), c_int(D), c_int(F), c_int(E), c_int(top), _ptr(error_flag(x.device)), _stream()),
+        "experts_grouped_bf16", kernels=4)
+    return y
+
+
+GROUPED_MIN_TOKENS = 33      # from here on the pairs are sorted and multiplied expert by expert on the tensor cores
+
+
+def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, grouped: Optional[bool] = None) -> torch.Tensor:
+    """The experts' outputs added up with the router's weights, by the kernels that suit the step: a few tokens (and
+    float32) read only the chosen experts' weights row by row; many bf16 tokens go through the grouped products.
+    `workspace` (parts.base.Workspace) lends the scratch; without it the scratch is allocated."""
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F, top = F2 // 2, ids.shape[1]
+    if grouped is None:
+        grouped = T >= GROUPED_MIN_TOKENS
+    grouped = grouped and experts_grouped_supported(x.dtype, D, F)
+
+    def scratch(name, rows_, width, dtype):
+        if workspace is not None:
+            return workspace.rows(name, rows_, width, dtype)
+        return torch.empty((rows_, width), dtype=dtype, device=x.device)
+
+    hid = scratch("moe_hidden", T, top * F, x.dtype)
+    if not grouped:
+        return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down)
+    rows_ = scratch("moe_rows", T, top * D, x.dtype)
+    sorted_pairs = scratch("moe_sorted", T, top, torch.int32)
+    slot_of = scratch("moe_slot_of", T, top, torch.int32)
+    if workspace is not None:
+        offsets = workspace.flat(f"moe_offsets_{E}", E + 1, torch.int32)
+    else:
+        offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
+    return experts_grouped_bf16(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows_)
 
 
 # ---- projection epilogue: per-head norm, rotary, cache write --------------------------------------------------

@@ -28,7 +28,7 @@ __global__ void embed_positions_kernel(float* __restrict__ out, float* __restric
         if (threadIdx.x == 0) atomicExch(err, 1);
         tok = tok < 0 ? 0 : V - 1;
     }
-    if (pos < 0 || pos >= P) {
+    if (pos_table != nullptr && (pos < 0 || pos >= P)) {
         if (threadIdx.x == 0) atomicExch(err, 3);
         pos = pos < 0 ? 0 : P - 1;
     }

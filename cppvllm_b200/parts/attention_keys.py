@@ -9,7 +9,9 @@
 No rotation: positions enter only through the mask.  The first ``keep_first`` positions stay visible after the window has
 passed them; the cache manager keeps their pages and gives the others back as the window passes.  All sizes and the
 scale are parameters.  Prompt portions and decoded tokens run through the same kernels: every token attends to its
-request's pages, which already hold the step's own keys.
+request's pages, which already hold the step's own keys.  bf16 with head sizes that are multiples of 16 (up to 128) runs
+on the tensor cores (csrc/attention_keys.cu: one tile of keys in shared memory feeds both products); float32 and other
+shapes take the general kernel (csrc/attention_general.cu).
 """
 from __future__ import annotations
 
@@ -77,6 +79,13 @@ class KeysAttention(Mixer):
         return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
 
     def attend(self, att, qk, ctx, cache, g):
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        if not self.force_general and ops.attn_keys_supported(qk.dtype, H, KV, hd, qk.shape[1]):
+            q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * ctx.num_seqs
+            ops.attn_keys_bf16(att, qk, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
+                               ops.attn_keys_tiles(q_lens, H, KV), H, KV, hd, g.page_size, self.scale, window=self.window,
+                               keep_first=self.keep_first)
+            return
         ops.paged_attention_general(att, qk, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions, self.num_heads,
                                     self.num_kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,
                                     num_tokens=ctx.num_tokens, keep_first=self.keep_first, keys_are_values=True)

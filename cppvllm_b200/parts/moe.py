@@ -5,7 +5,9 @@
   the ``top`` experts with the largest logits, weighted by the softmax over the chosen logits only; an expert is
   Wdown (silu(Wgate x) * (Wup x)) without biases; the output is the weighted sum of the chosen experts' outputs.  Expert e's
   tensors are ``<prefix>e<e>.gate|up|down``; they are stacked at load time into [E, 2 ff, D] (gate rows over up rows) and
-  [E, D, ff], so that a kernel reaches every expert from one base address.
+  [E, D, ff], so that a kernel reaches every expert from one base address.  A few tokens read only their chosen experts'
+  weights (two kernels spread over all SMs); many tokens are sorted by expert on the device and go through two grouped
+  products on the tensor cores (csrc/moe.cu); nothing travels to the host, so steps stay capturable.
 """
 from __future__ import annotations
 
@@ -94,4 +96,5 @@ class RoutedGLU(FeedForward):
         weights = ws.rows("moe_weights", T, self.top, torch.float32)
         ops.route_topk(ids, weights, x, self.w_router, self.b_router)
         y = ws.rows("ffn_out", T, self.hidden_size, x.dtype)
-        return ops.expert_rows(y, x, ids, weights, self.w_gate_up, self.w_down)
+        return ops.routed_experts(y, x, ids, weights, self.w_gate_up, self.w_down, workspace=ws,
+                                  grouped=False if self.rt.plain_kernels else None)
