@@ -103,6 +103,7 @@ attn_keys_kernel(const KeysAttnParams p) {
     auto load_tile = [&](int it, int stage) {
         const int key0 = (it < n_kept ? it : first_tile + it - n_kept) * kTileKeys;
         __nv_bfloat16* dst = sK + stage * kTileKeys * LD;
+        int last_slot = -1, page = -1;                    // a thread's rows ascend: the block table is read once per page
         for (int i = threadIdx.x; i < kTileKeys * CPR; i += kKeysThreads) {
             const int r = i / CPR, c = i - r * CPR;
             const int j = key0 + r;
@@ -110,7 +111,7 @@ attn_keys_kernel(const KeysAttnParams p) {
             const __nv_bfloat16* src = p.pages;
             if (need) {
                 const int slot = j / p.page_size;
-                const int page = slot < p.table_width ? table[slot] : -1;
+                if (slot != last_slot) { page = slot < p.table_width ? table[slot] : -1; last_slot = slot; }
                 if (page < 0 || page >= p.num_pages) {
                     atomicExch(p.err, 4);                 // a key a token of this block must see has no page
                     need = false;
@@ -252,6 +253,214 @@ attn_keys_kernel(const KeysAttnParams p) {
     }
 }
 
+// ---- decoded tokens: one token per request ---------------------------------------------------------------------------
+//
+// A block owns one (request, kv head): the g <= 16 query heads of the group are the rows of ONE 16-row slab, so the eight
+// warps have nothing to share but the keys, and each takes every eighth key tile (32 keys) for itself: it fetches its tiles
+// into two stages of its own (cp.async by its own lanes, __syncwarp, no block-wide barrier in the loop), keeps its own
+// running maximum, sum and accumulator, and the eight partial results are merged through shared memory at the end.  Up to
+// sixteen tiles are in flight per block.  Eight warps of short tiles rather than four of long ones: with one warp per
+// scheduler every instruction's latency shows (measured: 14 k instructions a warp in 90 k cycles, stalled on fixed-latency
+// dependencies), two warps per scheduler with half the instructions each overlap.
+constexpr int kDecWarps = 8;
+constexpr int kDecKeys = 32;                             // keys per tile of the decode form
+
+template <int HD>
+__global__ void __launch_bounds__(kDecWarps * 32)
+attn_keys_decode_kernel(const KeysAttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int LD = HD + 8;
+    constexpr int CPR = HD / 8;
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [16][LD]
+    __nv_bfloat16* sK = sQ + 16 * LD;                                                  // [warps][2][64][LD]
+    float* red_ml = reinterpret_cast<float*>(sK + kDecWarps * 2 * kDecKeys * LD);     // [warps][16][2]
+    const int g = p.H / p.KV;
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = p.cu_seqlens[seq];
+    const int pos = p.positions[t];
+    const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
+    const int key_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int keep = p.window > 0 ? p.keep_first : 0;
+    const int first_tile = key_lo / kDecKeys;
+    const int n_win = pos / kDecKeys - first_tile + 1;
+    const int n_kept = keep > 0 ? min((keep - 1) / kDecKeys + 1, first_tile) : 0;
+    const int n_tiles = n_kept + n_win;
+
+    for (int i = threadIdx.x; i < 16 * CPR; i += kDecWarps * 32) {
+        const int r = i / CPR, c = i - r * CPR;
+        const bool valid = r < g;
+        cp_async16(sQ + r * LD + c * 8, valid ? p.q + static_cast<int64_t>(t) * p.q_stride + (kvh * g + r) * HD + c * 8 : p.q, valid);
+    }
+    cp_async_commit();
+
+    __nv_bfloat16* my = sK + warp * 2 * kDecKeys * LD;
+    auto load_tile = [&](int it, int stage) {
+        const int key0 = (it < n_kept ? it : first_tile + it - n_kept) * kDecKeys;
+        __nv_bfloat16* dst = my + stage * kDecKeys * LD;
+        int last_slot = -1, page = -1;
+        for (int i = lane; i < kDecKeys * CPR; i += 32) {
+            const int r = i / CPR, c = i - r * CPR;
+            const int j = key0 + r;
+            bool need = j <= pos && (j >= key_lo || j < keep);
+            const __nv_bfloat16* src = p.pages;
+            if (need) {
+                const int slot = j / p.page_size;
+                if (slot != last_slot) { page = slot < p.table_width ? table[slot] : -1; last_slot = slot; }
+                if (page < 0 || page >= p.num_pages) {
+                    atomicExch(p.err, 4);
+                    need = false;
+                } else {
+                    src = p.pages + ((static_cast<int64_t>(page) * p.KV + kvh) * p.page_size + (j - slot * p.page_size)) * HD + c * 8;
+                }
+            }
+            cp_async16(dst + r * LD + c * 8, src, need);
+        }
+    };
+
+    const int my_tiles = (n_tiles - warp + kDecWarps - 1) / kDecWarps;     // tiles warp, warp + 4, ...
+    if (my_tiles > 0) load_tile(warp, 0);
+    cp_async_commit();
+    cp_async_wait<1>();                                   // this thread's share of the queries
+    __syncthreads();                                      // everybody's share
+    uint32_t qf[HD / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) ldm_x4(qf[ks], sQ + (lane & 15) * LD + ks * 16 + (lane >> 4) * 8);
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < HD / 8; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+
+    for (int n = 0; n < my_tiles; ++n) {
+        const int it = warp + n * kDecWarps;
+        if (n + 1 < my_tiles) load_tile(it + kDecWarps, (n + 1) & 1);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncwarp();
+        const int key0 = (it < n_kept ? it : first_tile + it - n_kept) * kDecKeys;
+        const __nv_bfloat16* tile = my + (n & 1) * kDecKeys * LD;
+        float s[kDecKeys / 8][4];
+#pragma unroll
+        for (int nt = 0; nt < kDecKeys / 8; ++nt) { s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f; }
+#pragma unroll
+        for (int ks = 0; ks < HD / 16; ++ks) {
+#pragma unroll
+            for (int np = 0; np < kDecKeys / 16; ++np) {
+                uint32_t b[4];
+                ldm_x4(b, tile + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * LD + ks * 16 + ((lane >> 3) & 1) * 8);
+                mma_16816(s[np * 2], qf[ks], b[0], b[1]);
+                mma_16816(s[np * 2 + 1], qf[ks], b[2], b[3]);
+            }
+        }
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < kDecKeys / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int j = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
+                const bool sees = j <= pos && (j >= key_lo || j < keep);
+                const float v = sees ? s[nt][e] * p.scale_log2 : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        }
+        float corr[2];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 1));
+            mx[half] = fmaxf(mx[half], __shfl_xor_sync(0xffffffffu, mx[half], 2));
+            const float m_new = fmaxf(m[half], mx[half]);
+            corr[half] = (m[half] == -INFINITY) ? 0.f : ex2(m[half] - m_new);
+            m[half] = m_new;
+        }
+        float sum[2] = {0.f, 0.f};
+#pragma unroll
+        for (int nt = 0; nt < kDecKeys / 8; ++nt) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pj = (s[nt][e] == -INFINITY) ? 0.f : ex2(s[nt][e] - m[e >> 1]);
+                s[nt][e] = pj;
+                sum[e >> 1] += pj;
+            }
+        }
+#pragma unroll
+        for (int half = 0; half < 2; ++half) l[half] = l[half] * corr[half] + sum[half];
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; ++dt) {
+            o[dt][0] *= corr[0]; o[dt][1] *= corr[0]; o[dt][2] *= corr[1]; o[dt][3] *= corr[1];
+        }
+#pragma unroll
+        for (int kk = 0; kk < kDecKeys / 16; ++kk) {
+            uint32_t a[4];
+            a[0] = pack2(s[kk * 2][0], s[kk * 2][1]);
+            a[1] = pack2(s[kk * 2][2], s[kk * 2][3]);
+            a[2] = pack2(s[kk * 2 + 1][0], s[kk * 2 + 1][1]);
+            a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
+#pragma unroll
+            for (int dp = 0; dp < HD / 16; ++dp) {
+                uint32_t b[4];
+                ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 + ((lane >> 4) & 1) * 8);
+                mma_16816(o[dp * 2], a, b[0], b[1]);
+                mma_16816(o[dp * 2 + 1], a, b[2], b[3]);
+            }
+        }
+        __syncwarp();                                     // the stage may be filled again
+    }
+    cp_async_wait<0>();
+
+    // merge the four warps' parts: each leaves its sums, maxima and its accumulator [16][HD] (float) in its own stages
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        l[half] += __shfl_xor_sync(0xffffffffu, l[half], 1);
+        l[half] += __shfl_xor_sync(0xffffffffu, l[half], 2);
+    }
+    __syncwarp();
+    float* part = reinterpret_cast<float*>(my);            // 16 * HD floats = 64 * HD bytes, within the warp's two stages (2 * 32 * LD * 2)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+        const int r = (lane >> 2) + half * 8;
+        if ((lane & 3) == 0) { red_ml[(warp * 16 + r) * 2] = m[half]; red_ml[(warp * 16 + r) * 2 + 1] = l[half]; }
+#pragma unroll
+        for (int dt = 0; dt < HD / 8; ++dt) {
+            const int d = dt * 8 + ((lane & 3) << 1);
+            part[r * HD + d] = o[dt][half * 2];
+            part[r * HD + d + 1] = o[dt][half * 2 + 1];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < g * HD; i += kDecWarps * 32) {
+        const int r = i / HD, d = i - r * HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
+        float ll = 0.f, acc = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecWarps; ++w) {
+            const float mw = red_ml[(w * 16 + r) * 2];
+            const float f = mw == -INFINITY ? 0.f : ex2(mw - mm);
+            ll += red_ml[(w * 16 + r) * 2 + 1] * f;
+            acc += reinterpret_cast<const float*>(sK + w * 2 * kDecKeys * LD)[r * HD + d] * f;
+        }
+        p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    }
+}
+
+template <int HD>
+int launch_attn_keys_decode(const KeysAttnParams& p, cudaStream_t stream) {
+    const size_t smem = static_cast<size_t>(16 + kDecWarps * 2 * kDecKeys) * (HD + 8) * sizeof(__nv_bfloat16) + kDecWarps * 16 * 2 * sizeof(float);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(attn_keys_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return launch_status();
+        raised = true;
+    }
+    launch_kernel(attn_keys_decode_kernel<HD>, dim3(p.S, p.KV), dim3(kDecWarps * 32), smem, stream, p);
+    return launch_status();
+}
+
 template <int HD>
 int launch_attn_keys(const KeysAttnParams& p, int num_tiles, cudaStream_t stream) {
     const size_t smem = static_cast<size_t>(kTileRows + 2 * kTileKeys) * (HD + 8) * sizeof(__nv_bfloat16);
@@ -277,7 +486,7 @@ extern "C" int cvb_attn_keys_supported(int H, int KV, int hd) {
 extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const void* pages, const int* block_tables,
                                   int table_width, const int* cu_seqlens, const int* positions, int S, int num_tiles, int H,
                                   int KV, int hd, int page_size, int window, int keep_first, float scale, int num_pages,
-                                  int* err_flag, cudaStream_t stream) {
+                                  int all_single, int* err_flag, cudaStream_t stream) {
     if (num_tiles == 0 || S == 0) return CVB_OK;
     if (S < 0 || num_tiles < 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || window < 0 || keep_first < 0) return CVB_E_SIZE;
     if (!cvb_attn_keys_supported(H, KV, hd)) return CVB_E_UNSUPPORTED;
@@ -293,6 +502,19 @@ extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const 
     p.window = window; p.keep_first = keep_first; p.num_pages = num_pages;
     p.scale_log2 = scale * kLog2eKeys;
     p.err = err_flag;
+    if (all_single && H / KV <= 16) {                     // every request brings one token: the kernel for decoded tokens
+        switch (hd) {
+            case 16: return launch_attn_keys_decode<16>(p, stream);
+            case 32: return launch_attn_keys_decode<32>(p, stream);
+            case 48: return launch_attn_keys_decode<48>(p, stream);
+            case 64: return launch_attn_keys_decode<64>(p, stream);
+            case 80: return launch_attn_keys_decode<80>(p, stream);
+            case 96: return launch_attn_keys_decode<96>(p, stream);
+            case 112: return launch_attn_keys_decode<112>(p, stream);
+            case 128: return launch_attn_keys_decode<128>(p, stream);
+        }
+        return CVB_E_UNSUPPORTED;
+    }
     switch (hd) {
         case 16: return launch_attn_keys<16>(p, num_tiles, stream);
         case 32: return launch_attn_keys<32>(p, num_tiles, stream);

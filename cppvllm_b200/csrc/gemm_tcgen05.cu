@@ -20,6 +20,9 @@
 //   warps 2-5 epilogue: each reads its 32 lanes of the accumulator with tcgen05.ld (32 columns at a time), applies the
 //            epilogue in float, rounds to bf16 once, stages boxes of 32 rows by 64 columns in shared memory for TMA
 //            stores (cp.async.bulk.tensor, whole lines, clipped at the edges) and hands the accumulator back.
+// Grouped form (a mixture of experts): the rows of A are sorted by expert into segments that start on multiples of 128
+// rows, a device table names the expert of every row tile, and the producer fetches the B tile from that expert's rows of
+// a weight that holds all experts' matrices one below the other; tiles without rows are skipped by all three roles.
 // Every wait on an mbarrier is bounded by a cycle count; a wait that runs out records error 5 and the block carries
 // on to its end (tensor memory is always given back).  No cluster launch, no multicast.
 #include "sm100.cuh"
@@ -41,6 +44,11 @@ struct GemmParams {
     int n_out;                // output columns: N, or N / 2 with SwiGLU
     int tiles_m, tiles_n, num_tiles;
     int* err;
+    // grouped form (tile_expert != nullptr): W holds the matrices of several experts one below the other, `expert_rows`
+    // rows each; row tile i of A and of the output (128 rows) belongs to expert tile_expert[i] and is multiplied by that
+    // expert's matrix; a tile whose entry is negative holds no rows and is skipped by every role alike
+    const int* tile_expert;
+    int expert_rows;
 };
 
 // Tile t of the walk: groups of kGroupM row tiles are finished one after the other, and within a group the row tile runs
@@ -110,6 +118,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
                 int m0, n0;
                 tile_origin(t, p, OUT_COLS, m0, n0);
+                int w0 = 0;                            // first row of this tile's expert in W
+                if (p.tile_expert != nullptr) {
+                    const int e = p.tile_expert[m0 / kBM];
+                    if (e < 0) continue;
+                    w0 = e * p.expert_rows;
+                }
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (it >= STAGES) mbar_wait(empty + s, ((it / STAGES) - 1) & 1, p.err);
@@ -117,17 +131,23 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                     unsigned char* b_dst = a_dst + L::kABytes;
                     mbar_expect_tx(full + s, L::kStageBytes);
                     tma_load_2d(a_dst, &map_a, full + s, kb * kBK, m0);
-                    tma_load_2d(b_dst, &map_w, full + s, kb * kBK, n0);
-                    if constexpr (SWIGLU) tma_load_2d(b_dst + 128 * kBK * 2, &map_w, full + s, kb * kBK, p.n_out + n0);
-                    else if constexpr (BN == 256) tma_load_2d(b_dst + 128 * kBK * 2, &map_w, full + s, kb * kBK, n0 + 128);
+                    tma_load_2d(b_dst, &map_w, full + s, kb * kBK, w0 + n0);
+                    if constexpr (SWIGLU) tma_load_2d(b_dst + 128 * kBK * 2, &map_w, full + s, kb * kBK, w0 + p.n_out + n0);
+                    else if constexpr (BN == 256) tma_load_2d(b_dst + 128 * kBK * 2, &map_w, full + s, kb * kBK, w0 + n0 + 128);
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {                               // ---- tensor-core issue ----
             constexpr uint32_t idesc = idesc_bf16(kBM, BN, false);
-            int it = 0, i = 0;
-            for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++i) {
+            int it = 0, i = -1;
+            for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
+                if (p.tile_expert != nullptr) {
+                    int m0, n0;
+                    tile_origin(t, p, SWIGLU ? BN / 2 : BN, m0, n0);
+                    if (p.tile_expert[m0 / kBM] < 0) continue;
+                }
+                ++i;
                 const int buf = i & 1, use = i >> 1;
                 if (use > 0) {                         // the epilogue of the tile before last has drained this accumulator
                     mbar_wait(acc_free + buf, (use - 1) & 1, p.err);
@@ -156,11 +176,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // at the matrix's edges.  Two boxes per warp, so that one is stored while the next is filled.
         const int quarter = warp & 3;
         unsigned char* boxes = staging + (warp - 2) * (2 * kBoxBytes);
-        int i = 0, n_box = 0;
-        for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++i) {
-            const int buf = i & 1, use = i >> 1;
+        int i = -1, n_box = 0;
+        for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x) {
             int m0, n0;
             tile_origin(t, p, OUT_COLS, m0, n0);
+            if (p.tile_expert != nullptr && p.tile_expert[m0 / kBM] < 0) continue;
+            ++i;
+            const int buf = i & 1, use = i >> 1;
             const int row = m0 + quarter * 32 + lane;
             const uint32_t tmem_d = tmem_base + buf * BN + (static_cast<uint32_t>(quarter * 32) << 16);
             mbar_wait(acc_ready + buf, use & 1, p.err);
@@ -295,4 +317,33 @@ extern "C" int cvb_gemm_bf16_tcgen05(void* out, const void* a, const void* w, co
     if (mode == 0) return tile_n == 256 ? launch_gemm<256, 4, kPlain>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kPlain>(ma, mw, mo, p, stream);
     if (mode == 2) return tile_n == 256 ? launch_gemm<256, 4, kAddResidual>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kAddResidual>(ma, mw, mo, p, stream);
     return CVB_E_SHAPE;
+}
+
+// The grouped form: A [M, K] holds the rows of E experts in segments that start on multiples of 128 rows; row tile i
+// belongs to expert tile_expert[i] (device memory, negative: no rows); W [E * N, K] holds the experts' matrices one below
+// the other.  mode 0: C[M, N] = A W_e^T per tile;  mode 1: C[M, N / 2] = silu(A Wg_e^T) * (A Wu_e^T), W_e = [Wg_e; Wu_e].
+extern "C" int cvb_gemm_grouped_bf16_tcgen05(void* out, const void* a, const void* w, const int* tile_expert, int M, int N, int E,
+                                             int K, int mode, int tile_n, int* err_flag, cudaStream_t stream) {
+    if (M == 0) return CVB_OK;
+    if (M < 0 || N <= 0 || K <= 0 || E <= 0 || tile_expert == nullptr) return CVB_E_SIZE;
+    if (K % 8 || M % kBM) return CVB_E_ALIGN;
+    auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al(out) || !al(a) || !al(w)) return CVB_E_ALIGN;
+    if (mode != 0 && mode != 1) return CVB_E_SHAPE;
+    if (mode == 1 && (N % 2)) return CVB_E_SHAPE;
+    if (static_cast<int64_t>(E) * N > 2147483647LL) return CVB_E_SIZE;
+    GemmParams p{};
+    p.out = (__nv_bfloat16*)out; p.resid = nullptr; p.M = M; p.N = N; p.K = K;
+    p.n_out = mode == 1 ? N / 2 : N; p.err = err_flag;
+    p.tile_expert = tile_expert; p.expert_rows = N;
+    if (p.n_out % 8) return CVB_E_ALIGN;
+    CUtensorMap ma, mw, mo;
+    int rc = matrix_map(&ma, a, M, K);
+    if (rc != CVB_OK) return rc;
+    rc = matrix_map(&mw, w, static_cast<int64_t>(E) * N, K);
+    if (rc != CVB_OK) return rc;
+    rc = cached_bf16_map(&mo, out, M, p.n_out, 64, 32);
+    if (rc != CVB_OK) return rc;
+    if (mode == 1) return launch_gemm<256, 4, kSwiglu>(ma, mw, mo, p, stream);
+    return tile_n == 256 ? launch_gemm<256, 4, kPlain>(ma, mw, mo, p, stream) : launch_gemm<128, 6, kPlain>(ma, mw, mo, p, stream);
 }

@@ -11,14 +11,13 @@
 //   bounds such a step, with the work of a (token, expert) pair spread over many blocks so that every SM streams:
 //     expert_hidden : block (pair, slice of ff): a warp owns inner elements, its lanes a row of the gate and of the up weight
 //     expert_down   : block (token, slice of D): walks the token's experts, a warp owns output elements
-//   Many tokens (prompt portions, bf16): the (token, expert) pairs are sorted by expert on the device (sort_pairs: counts,
-//   offsets, a permutation; no trip to the host, so the step stays capturable), then two grouped products on the tensor
-//   cores (grouped_gemm: tiles of 64 rows of ONE expert by 64 outputs, `mma.sync.m16n8k16` bf16 with float accumulation,
-//   operands by cp.async into two stages; the rows of x are gathered through the permutation as they are loaded, so no
-//   sorted copy of x exists; gate and up rows of the same inner elements share a tile, so the gated activation is the
-//   epilogue), and a kernel that adds a token's expert outputs up with its weights.
+//   More tokens (bf16; from a handful of tokens that share experts up to prompt portions): the (token, expert) pairs are
+//   sorted by expert on the device (sort_pairs_padded: counts, every expert's segment on a multiple of 128 rows, the
+//   expert of every row tile; no trip to the host, so the step stays capturable), the tokens' rows are gathered into that
+//   order, two grouped products run on the tcgen05 kernel (gemm_tcgen05.cu, grouped form: gate and up rows share a tile,
+//   so the gated activation is the epilogue; every chosen expert's weights are read once, experts nobody chose cost
+//   nothing), and combine_pairs adds a token's expert outputs up with its weights.
 #include "common.cuh"
-#include "sm100.cuh"
 
 namespace cvb {
 
@@ -77,6 +76,28 @@ constexpr int kExpertWarps = kExpertThreads / 32;
 
 template <typename T> __device__ __forceinline__ float silu_exact(float g) { return g / (1.f + expf(-g)); }
 
+// Eight weights of a bf16 row against eight floats in shared memory: one 16-byte load per lane and row.
+__device__ __forceinline__ float dot8(const __nv_bfloat16* __restrict__ w, const float* __restrict__ xs, float acc) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(w);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float4 x0 = *reinterpret_cast<const float4*>(xs), x1 = *reinterpret_cast<const float4*>(xs + 4);
+    float2 f = __bfloat1622float2(h[0]);
+    acc = fmaf(x0.x, f.x, acc); acc = fmaf(x0.y, f.y, acc);
+    f = __bfloat1622float2(h[1]);
+    acc = fmaf(x0.z, f.x, acc); acc = fmaf(x0.w, f.y, acc);
+    f = __bfloat1622float2(h[2]);
+    acc = fmaf(x1.x, f.x, acc); acc = fmaf(x1.y, f.y, acc);
+    f = __bfloat1622float2(h[3]);
+    acc = fmaf(x1.z, f.x, acc); acc = fmaf(x1.w, f.y, acc);
+    return acc;
+}
+template <typename T> __device__ __forceinline__ bool rows_by_16_bytes(const T*, int) { return false; }
+template <> __device__ __forceinline__ bool rows_by_16_bytes<__nv_bfloat16>(const __nv_bfloat16* base, int row_len) {
+    return row_len % 8 == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0;
+}
+template <typename T> __device__ __forceinline__ float dot8_of(const T*, const float*, float acc) { return acc; }
+template <> __device__ __forceinline__ float dot8_of<__nv_bfloat16>(const __nv_bfloat16* w, const float* xs, float acc) { return dot8(w, xs, acc); }
+
 // hid[pair, f] = T(silu(Wg_e[f] . x) * (Wu_e[f] . x)) for the block's slice of f; pair = t * top + k, e = ids[pair]
 template <typename T>
 __global__ void __launch_bounds__(kExpertThreads)
@@ -84,7 +105,7 @@ expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __
                      int D, int F, int E, int top, int per_block, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     float* xs = smem;                                   // [D]
     const int64_t pair = blockIdx.x;
     const int64_t t = pair / top;
@@ -99,6 +120,7 @@ expert_hidden_kernel(T* __restrict__ hid, const T* __restrict__ x, const int* __
     const T* g_rows = wgu + static_cast<int64_t>(e) * 2 * F * D;
     const T* u_rows = g_rows + static_cast<int64_t>(F) * D;
     const int f0 = blockIdx.y * per_block, f1 = min(F, f0 + per_block);
+    const bool wide = rows_by_16_bytes<T>(wgu, D);
     for (int f = f0 + warp; f < f1; f += kExpertWarps) {
         const T* gr = g_rows + static_cast<int64_t>(f) * D;
         const T* ur = u_rows + static_cast<int64_t>(f) * D;
@@ -121,13 +143,14 @@ expert_down_kernel(T* __restrict__ y, const T* __restrict__ hid, const int* __re
                    const T* __restrict__ wd, int D, int F, int E, int top, int per_block) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float smem[];
+    extern __shared__ __align__(16) float smem[];
     float* hs = smem;                                   // [F]
     float* acc = hs + F;                                // [per_block]
     const int64_t t = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int d0 = blockIdx.y * per_block, d1 = min(D, d0 + per_block);
     for (int i = threadIdx.x; i < per_block; i += kExpertThreads) acc[i] = 0.f;
+    const bool wide = rows_by_16_bytes<T>(wd, F);
     for (int k = 0; k < top; ++k) {
         int e = ids[t * top + k];
         if (e < 0 || e >= E) e = 0;                      // reported by the kernel in front
@@ -139,7 +162,11 @@ expert_down_kernel(T* __restrict__ y, const T* __restrict__ hid, const int* __re
         for (int d = d0 + warp; d < d1; d += kExpertWarps) {
             const T* dr = d_rows + static_cast<int64_t>(d) * F;
             float o = 0.f;
-            for (int i = lane; i < F; i += 32) o = fmaf(hs[i], to_float(dr[i]), o);
+            if (wide) {
+                for (int i = lane * 8; i < F; i += 256) o = dot8_of<T>(dr + i, hs + i, o);
+            } else {
+                for (int i = lane; i < F; i += 32) o = fmaf(hs[i], to_float(dr[i]), o);
+            }
             o = warp_sum(o);
             if (lane == 0) acc[d - d0] = fmaf(wk, o, acc[d - d0]);     // a warp owns its d: no other warp touches acc[d - d0]
         }
@@ -152,17 +179,21 @@ expert_down_kernel(T* __restrict__ y, const T* __restrict__ hid, const int* __re
 
 constexpr int kSortThreads = 1024;
 
-// counts per expert, offsets (exclusive prefix, [E + 1]), and the permutation: sorted[slot] = pair, slot_of[pair] = slot.
-// One block.  The order of an expert's rows among themselves is not fixed; no result depends on it.
+// Counts per expert, then every expert's segment of sorted rows, which starts on a multiple of `pad` rows (the tcgen05
+// grouped product's row tiles are 128 rows of ONE expert).  One block.  The order of an expert's rows among themselves
+// is not fixed; no result depends on it.  tile_expert[i]: the expert of row tile i, -1 for tiles behind the last segment (max_tiles
+// entries).  row_token[slot]: the token whose row goes to sorted row `slot` (0 for the padding rows: they are computed
+// and never read).  slot_of[pair]: where the pair's row lies.
 __global__ void __launch_bounds__(kSortThreads)
-sort_pairs_kernel(int* __restrict__ offsets, int* __restrict__ sorted, int* __restrict__ slot_of, const int* __restrict__ ids,
-                  int n_pairs, int E, int* __restrict__ err) {
+sort_pairs_padded_kernel(int* __restrict__ tile_expert, int* __restrict__ row_token, int* __restrict__ slot_of,
+                         const int* __restrict__ ids, int n_pairs, int E, int top, int pad, int max_tiles, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
     extern __shared__ int ismem[];
     int* count = ismem;                                 // [E]
     int* start = count + E;                             // [E + 1]
     for (int e = threadIdx.x; e < E; e += kSortThreads) count[e] = 0;
+    for (int i = threadIdx.x; i < max_tiles * pad; i += kSortThreads) row_token[i] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n_pairs; i += kSortThreads) {
         int e = ids[i];
@@ -172,135 +203,31 @@ sort_pairs_kernel(int* __restrict__ offsets, int* __restrict__ sorted, int* __re
     __syncthreads();
     if (threadIdx.x == 0) {
         int run = 0;
-        for (int e = 0; e < E; ++e) { start[e] = run; run += count[e]; }
+        for (int e = 0; e < E; ++e) { start[e] = run; run += (count[e] + pad - 1) / pad * pad; }
         start[E] = run;
     }
     __syncthreads();
-    for (int e = threadIdx.x; e <= E; e += kSortThreads) offsets[e] = start[e];
+    for (int i = threadIdx.x; i < max_tiles; i += kSortThreads) {
+        int e = -1;
+        if (i * pad < start[E]) {
+            int lo = 0, hi = E - 1;                      // the last expert whose segment starts at or before the tile
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (start[mid] <= i * pad) lo = mid; else hi = mid - 1;
+            }
+            e = lo;
+            while (e < E - 1 && start[e + 1] <= i * pad) ++e;      // empty experts share a start: take the one that has rows
+        }
+        tile_expert[i] = e;
+    }
     for (int e = threadIdx.x; e < E; e += kSortThreads) count[e] = 0;
     __syncthreads();
     for (int i = threadIdx.x; i < n_pairs; i += kSortThreads) {
         int e = ids[i];
         if (e < 0 || e >= E) e = 0;
         const int slot = start[e] + atomicAdd(&count[e], 1);
-        sorted[slot] = i;
+        row_token[slot] = i / top;
         slot_of[i] = slot;
-    }
-}
-
-constexpr int kGemmThreads = 128;
-constexpr int kGM = 64, kGN = 64, kGK = 32, kGLD = kGK + 8;
-
-__device__ __forceinline__ void g_ldm_x4(uint32_t (&r)[4], const void* p) {
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
-}
-__device__ __forceinline__ void g_mma(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-
-// out[r, n] for the sorted rows r of one expert e:  A row r is a[(gather ? gather[r] / top : r)] (K elements), B is expert
-// e's matrix [N_rows, K] at b + e * b_stride.
-//   GATED: the tile's 64 columns are 32 gate rows n0..n0+31 and the 32 up rows F + n0..; out[r, n0 + c] = silu(gate) * up
-//   else : 64 rows n0..n0+63; out[r, n0 + c] = the product
-// Block (tile of rows, slice of n).  Tiles are numbered expert by expert: ceil(count_e / 64) each; a block beyond the last
-// tile returns.
-template <bool GATED>
-__global__ void __launch_bounds__(kGemmThreads)
-grouped_gemm_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ a, const int* __restrict__ gather, int top,
-                    const __nv_bfloat16* __restrict__ b, int64_t b_stride, const int* __restrict__ offsets, int E, int K, int N) {
-    pdl_trigger();
-    pdl_wait();
-    __shared__ __align__(16) __nv_bfloat16 sA[2][kGM * kGLD];
-    __shared__ __align__(16) __nv_bfloat16 sB[2][kGN * kGLD];
-    __shared__ int64_t a_row[kGM];
-    int e = 0, tile = blockIdx.x, r0 = 0, r1 = 0;
-    for (; e < E; ++e) {
-        const int lo = offsets[e], n = offsets[e + 1] - lo;
-        const int tiles = (n + kGM - 1) / kGM;
-        if (tile < tiles) { r0 = lo + tile * kGM; r1 = min(lo + n, r0 + kGM); break; }
-        tile -= tiles;
-    }
-    if (e >= E) return;
-    const int n_out = GATED ? kGN / 2 : kGN;             // output columns of this block
-    const int n0 = blockIdx.y * n_out;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int r = threadIdx.x; r < kGM; r += kGemmThreads) {
-        const int row = r0 + r;
-        a_row[r] = row < r1 ? static_cast<int64_t>(gather ? gather[row] / top : row) * K : -1;
-    }
-    __syncthreads();
-    const __nv_bfloat16* be = b + static_cast<int64_t>(e) * b_stride;
-
-    auto load = [&](int kt, int stage) {
-        const int k0 = kt * kGK;
-        for (int i = threadIdx.x; i < kGM * (kGK / 8); i += kGemmThreads) {
-            const int r = i / (kGK / 8), c = i % (kGK / 8);
-            const bool ok = a_row[r] >= 0 && k0 + c * 8 < K;
-            cp_async16(&sA[stage][r * kGLD + c * 8], ok ? a + a_row[r] + k0 + c * 8 : a, ok);
-        }
-        for (int i = threadIdx.x; i < kGN * (kGK / 8); i += kGemmThreads) {
-            const int r = i / (kGK / 8), c = i % (kGK / 8);
-            int n;                                       // the weight row behind column r of the tile
-            if (GATED) n = r < kGN / 2 ? n0 + r : N / 2 + n0 + (r - kGN / 2);
-            else n = n0 + r;
-            const bool in = GATED ? (n0 + (r % (kGN / 2)) < N / 2) : (n < N);
-            const bool ok = in && k0 + c * 8 < K;
-            cp_async16(&sB[stage][r * kGLD + c * 8], ok ? be + static_cast<int64_t>(n) * K + k0 + c * 8 : be, ok);
-        }
-    };
-
-    float acc[8][4];
-#pragma unroll
-    for (int nt = 0; nt < 8; ++nt) { acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f; }
-    const int n_k = (K + kGK - 1) / kGK;
-    load(0, 0);
-    cp_async_commit();
-    for (int kt = 0; kt < n_k; ++kt) {
-        if (kt + 1 < n_k) load(kt + 1, (kt + 1) & 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        const __nv_bfloat16* tA = sA[kt & 1];
-        const __nv_bfloat16* tB = sB[kt & 1];
-#pragma unroll
-        for (int ks = 0; ks < kGK / 16; ++ks) {
-            uint32_t af[4];
-            g_ldm_x4(af, tA + (warp * 16 + (lane & 15)) * kGLD + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-            for (int np = 0; np < 4; ++np) {
-                uint32_t bf[4];
-                g_ldm_x4(bf, tB + (np * 16 + (lane & 7) + ((lane >> 4) & 1) * 8) * kGLD + ks * 16 + ((lane >> 3) & 1) * 8);
-                g_mma(acc[np * 2], af, bf[0], bf[1]);
-                g_mma(acc[np * 2 + 1], af, bf[2], bf[3]);
-            }
-        }
-        __syncthreads();
-    }
-    const int out_width = GATED ? N / 2 : N;
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const int row = r0 + warp * 16 + (lane >> 2) + half * 8;
-        if (row >= r1) continue;
-        __nv_bfloat16* dst = out + static_cast<int64_t>(row) * out_width;
-#pragma unroll
-        for (int nt = 0; nt < (GATED ? 4 : 8); ++nt) {
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                const int col = n0 + nt * 8 + ((lane & 3) << 1) + c;
-                if (col >= out_width) continue;
-                float v;
-                if (GATED) {
-                    const float g = acc[nt][half * 2 + c], u = acc[nt + 4][half * 2 + c];
-                    v = g / (1.f + __expf(-g)) * u;
-                } else {
-                    v = acc[nt][half * 2 + c];
-                }
-                dst[col] = __float2bfloat16_rn(v);
-            }
-        }
     }
 }
 
@@ -365,27 +292,21 @@ extern "C" int cvb_expert_rows(void* y, void* hid, const void* x, const int* ids
     return launch_status();
 }
 
-// The grouped path (bf16): scratch `offsets` [E + 1], `sorted` and `slot_of` [T * top] ints, `hid` [T * top, F] and
-// `rows` [T * top, D] bf16.
-extern "C" int cvb_experts_grouped_bf16(void* y, const void* x, const int* ids, const float* weights, const void* wgu,
-                                        const void* wd, int* offsets, int* sorted, int* slot_of, void* hid, void* rows, int T,
-                                        int D, int F, int E, int top, int* err_flag, cudaStream_t stream) {
-    if (T == 0) return CVB_OK;
-    if (T < 0 || D <= 0 || F <= 0 || E <= 0 || top <= 0) return CVB_E_SIZE;
-    if (D % 8 != 0 || F % 8 != 0) return CVB_E_ALIGN;
-    const int64_t pairs64 = static_cast<int64_t>(T) * top;
-    if (pairs64 > (1 << 30) || E > 4096) return CVB_E_SIZE;
-    const int pairs = static_cast<int>(pairs64);
-    launch_kernel(sort_pairs_kernel, dim3(1), dim3(kSortThreads), (2 * static_cast<size_t>(E) + 1) * sizeof(int), stream, offsets,
-                  sorted, slot_of, ids, pairs, E, err_flag);
-    const int max_tiles = (pairs + kGM - 1) / kGM + E;     // sum over experts of ceil(count / 64) never exceeds this
-    launch_kernel(grouped_gemm_kernel<true>, dim3(max_tiles, (F + kGN / 2 - 1) / (kGN / 2)), dim3(kGemmThreads), 0, stream,
-                  (__nv_bfloat16*)hid, (const __nv_bfloat16*)x, (const int*)sorted, top, (const __nv_bfloat16*)wgu,
-                  static_cast<int64_t>(2) * F * D, (const int*)offsets, E, D, 2 * F);
-    launch_kernel(grouped_gemm_kernel<false>, dim3(max_tiles, (D + kGN - 1) / kGN), dim3(kGemmThreads), 0, stream,
-                  (__nv_bfloat16*)rows, (const __nv_bfloat16*)hid, (const int*)nullptr, 1, (const __nv_bfloat16*)wd,
-                  static_cast<int64_t>(D) * F, (const int*)offsets, E, F, D);
+// Sorts the pairs for the tcgen05 grouped product (see sort_pairs_padded_kernel); max_tiles * 128 rows of scratch.
+extern "C" int cvb_sort_pairs_padded(int* tile_expert, int* row_token, int* slot_of, const int* ids, int T, int E, int top,
+                                     int max_tiles, int* err_flag, cudaStream_t stream) {
+    if (T <= 0 || E <= 0 || top <= 0 || max_tiles <= 0 || E > 4096) return CVB_E_SIZE;
+    const int64_t pairs = static_cast<int64_t>(T) * top;
+    if (pairs > (1 << 30) || (pairs + 127) / 128 + E > max_tiles) return CVB_E_SCRATCH;
+    launch_kernel(sort_pairs_padded_kernel, dim3(1), dim3(kSortThreads), (2 * static_cast<size_t>(E) + 1) * sizeof(int), stream,
+                  tile_expert, row_token, slot_of, ids, static_cast<int>(pairs), E, top, 128, max_tiles, err_flag);
+    return launch_status();
+}
+
+extern "C" int cvb_combine_pairs_bf16(void* y, const void* rows, const int* slot_of, const float* weights, int T, int D, int top,
+                                      cudaStream_t stream) {
+    if (T <= 0 || D <= 0 || top <= 0) return CVB_E_SIZE;
     launch_kernel(combine_pairs_kernel, dim3(T), dim3(D >= 1024 ? 256 : 128), 0, stream, (__nv_bfloat16*)y,
-                  (const __nv_bfloat16*)rows, (const int*)slot_of, weights, D, top);
+                  (const __nv_bfloat16*)rows, slot_of, weights, D, top);
     return launch_status();
 }

@@ -321,9 +321,11 @@ def attn_keys_tiles(q_lens, num_heads: int, num_kv_heads: int) -> int:
 
 def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
                    positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                   page_size: int, scale: float, window: int = 0, keep_first: int = 0) -> torch.Tensor:
+                   page_size: int, scale: float, window: int = 0, keep_first: int = 0, all_single: bool = False) -> torch.Tensor:
     """Attention of prompt portions and decoded tokens over pages [kv head, slot, head_dim] whose keys are also the
-    values; `q` may be the packed output of a projection (rows of q.shape[1] elements, queries first)."""
+    values; `q` may be the packed output of a projection (rows of q.shape[1] elements, queries first).  `all_single`:
+    every request brings exactly one token (a decode step): a block per (request, kv head) whose warps share out the key
+    tiles among themselves."""
     _cuda(out, q, pages, block_tables, cu_seqlens, positions); _contig(out, q, pages, block_tables, cu_seqlens, positions)
     if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_keys_bf16 takes bf16 queries, pages and output")
@@ -333,8 +335,8 @@ def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, bloc
     _check(_attn_keys_lib().cvb_attn_keys_bf16(
         _ptr(out), _ptr(q), c_int(q.shape[1]), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), c_int(num_pages), _ptr(error_flag(q.device)),
-        _stream()), "attn_keys_bf16")
+        c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), c_int(num_pages), c_int(1 if all_single else 0),
+        _ptr(error_flag(q.device)), _stream()), "attn_keys_bf16")
     return out
 
 
@@ -347,7 +349,7 @@ def _moe_lib():
     global _moe
     if _moe is None:
         lib = load_library("moe")
-        for name in ("cvb_route_topk", "cvb_expert_rows", "cvb_experts_grouped_bf16"):
+        for name in ("cvb_route_topk", "cvb_expert_rows", "cvb_sort_pairs_padded", "cvb_combine_pairs_bf16"):
             getattr(lib, name).restype = c_int
         _moe = lib
     return _moe
@@ -393,59 +395,88 @@ def experts_grouped_supported(x_dtype: torch.dtype, D: int, F: int) -> bool:
     return x_dtype == torch.bfloat16 and D % 8 == 0 and F % 8 == 0
 
 
-def experts_grouped_bf16(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows) -> torch.Tensor:
-    """The same result for many tokens: pairs sorted by expert on the device, two grouped products on the tensor cores, and
-    the weighted sum.  Scratch: offsets int32 [E + 1], sorted_pairs and slot_of int32 [T * top], hid bf16 [T * top, ff],
-    rows bf16 [T * top, D]."""
-    _cuda(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows)
-    _contig(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows)
-    T, D = x.shape
-    E, F2, _ = w_gate_up.shape
-    F = F2 // 2
-    top = ids.shape[1]
-    bf = torch.bfloat16
-    if (any(t.dtype != bf for t in (y, x, w_gate_up, w_down, hid, rows)) or y.shape != x.shape or w_gate_up.shape != (E, 2 * F, D)
-            or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or weights.dtype != torch.float32 or ids.shape != weights.shape
-            or ids.shape[0] != T or any(t.dtype != torch.int32 for t in (offsets, sorted_pairs, slot_of)) or offsets.numel() < E + 1
-            or sorted_pairs.numel() < T * top or slot_of.numel() < T * top or hid.numel() < T * top * F or rows.numel() < T * top * D):
-        raise KernelError("experts_grouped_bf16: bf16 x, y, weights and scratch of the documented sizes; int32 index scratch")
-    _check(_moe_lib().cvb_experts_grouped_bf16(
-        _ptr(y), _ptr(x), _ptr(ids), _ptr(weights), _ptr(w_gate_up), _ptr(w_down), _ptr(offsets), _ptr(sorted_pairs), _ptr(slot_of),
-        _ptr(hid), _ptr(rows), c_int(T), c_int(D), c_int(F), c_int(E), c_int(top), _ptr(error_flag(x.device)), _stream()),
-        "experts_grouped_bf16", kernels=4)
-    return y
+def grouped_rows_tcgen05(num_tokens: int, top: int, num_experts: int) -> int:
+    """Rows of scratch the tcgen05 grouped path needs: every expert's segment starts on a multiple of 128 rows."""
+    return ((num_tokens * top + 127) // 128 + num_experts) * 128
 
 
-GROUPED_MIN_TOKENS = 33      # from here on the pairs are sorted and multiplied expert by expert on the tensor cores
-
-
-def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, grouped: Optional[bool] = None) -> torch.Tensor:
-    """The experts' outputs added up with the router's weights, by the kernels that suit the step: a few tokens (and
-    float32) read only the chosen experts' weights row by row; many bf16 tokens go through the grouped products.
-    `workspace` (parts.base.Workspace) lends the scratch; without it the scratch is allocated."""
+def experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows) -> torch.Tensor:
+    """More tokens on the tcgen05 tensor cores: the pairs are sorted by expert into segments that start on multiples of
+    128 rows (device side), the tokens' rows are gathered into that order, and two grouped products (the first with the
+    gated activation as its epilogue) run on csrc/gemm_tcgen05.cu's kernel; the last kernel adds a token's expert outputs
+    up with its weights.  Scratch: R = grouped_rows_tcgen05(T, top, E) rows: tile_expert int32 [R / 128], row_token int32 [R],
+    slot_of int32 [T * top], xs bf16 [R, D], hid bf16 [R, ff], rows bf16 [R, D]."""
+    global _gemm
+    _cuda(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows)
+    _contig(y, x, ids, weights, w_gate_up, w_down, tile_expert, row_token, slot_of, xs, hid, rows)
     T, D = x.shape
     E, F2, _ = w_gate_up.shape
     F, top = F2 // 2, ids.shape[1]
-    if grouped is None:
-        grouped = T >= GROUPED_MIN_TOKENS
-    grouped = grouped and experts_grouped_supported(x.dtype, D, F)
+    R = grouped_rows_tcgen05(T, top, E)
+    bf = torch.bfloat16
+    if (any(t.dtype != bf for t in (y, x, w_gate_up, w_down, xs, hid, rows)) or y.shape != x.shape or w_gate_up.shape != (E, 2 * F, D)
+            or w_down.shape != (E, D, F) or ids.dtype != torch.int32 or weights.dtype != torch.float32 or ids.shape != weights.shape
+            or any(t.dtype != torch.int32 for t in (tile_expert, row_token, slot_of)) or tile_expert.numel() < R // 128
+            or row_token.numel() < R or slot_of.numel() < T * top or xs.numel() < R * D or hid.numel() < R * F or rows.numel() < R * D):
+        raise KernelError("experts_grouped_tcgen05: bf16 x, y, weights and scratch of the documented sizes; int32 index scratch")
+    if _gemm is None:
+        lib = load_library("gemm_bf16")
+        lib.cvb_gemm_bf16_tcgen05.restype = c_int
+        _gemm = lib
+    _gemm.cvb_gemm_grouped_bf16_tcgen05.restype = c_int
+    err = _ptr(error_flag(x.device))
+    _check(_moe_lib().cvb_sort_pairs_padded(_ptr(tile_expert), _ptr(row_token), _ptr(slot_of), _ptr(ids), c_int(T), c_int(E), c_int(top),
+                                            c_int(R // 128), err, _stream()), "sort_pairs_padded")
+    xs2, hid2, rows2 = xs.view(-1)[:R * D].view(R, D), hid.view(-1)[:R * F].view(R, F), rows.view(-1)[:R * D].view(R, D)
+    gather_rows(xs2, x, row_token.view(-1)[:R])
+    _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(hid2), _ptr(xs2), _ptr(w_gate_up), _ptr(tile_expert), c_int(R), c_int(2 * F), c_int(E),
+                                               c_int(D), c_int(1), c_int(256), err, _stream()), "gemm_grouped_bf16_tcgen05")
+    tiles_256 = (T * top // 128 + 1) * ((D + 255) // 256)
+    _check(_gemm.cvb_gemm_grouped_bf16_tcgen05(_ptr(rows2), _ptr(hid2), _ptr(w_down), _ptr(tile_expert), c_int(R), c_int(D), c_int(E),
+                                               c_int(F), c_int(0), c_int(256 if tiles_256 >= 120 else 128), err, _stream()),
+           "gemm_grouped_bf16_tcgen05")
+    _check(_moe_lib().cvb_combine_pairs_bf16(_ptr(y), _ptr(rows2), _ptr(slot_of), _ptr(weights), c_int(T), c_int(D), c_int(top), _stream()),
+           "combine_pairs")
+    return y
 
-    def scratch(name, rows_, width, dtype):
-        if workspace is not None:
-            return workspace.rows(name, rows_, width, dtype)
-        return torch.empty((rows_, width), dtype=dtype, device=x.device)
 
-    hid = scratch("moe_hidden", T, top * F, x.dtype)
-    if not grouped:
-        return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down)
-    rows_ = scratch("moe_rows", T, top * D, x.dtype)
-    sorted_pairs = scratch("moe_sorted", T, top, torch.int32)
-    slot_of = scratch("moe_slot_of", T, top, torch.int32)
+def grouped_experts_preferred(num_pairs: int, num_experts: int, expert_bytes: int) -> bool:
+    """Whether a step's (token, expert) pairs go through the grouped tcgen05 products rather than pair by pair.  Pair by pair
+    reads an expert once per pair (the L2 absorbs repeats only for small experts) and costs two launches; grouped reads
+    every chosen expert once and costs five.  Measured on a B200 (8 experts of 9 MB, 2 per token: 4 tokens 28 against 34 us,
+    8 tokens 48 against 35; 8 experts of 151 MB: 1 token 92 against 110 us, 2 tokens 171 against 122, 8 tokens 623 against
+    218; 64 experts of 9 MB, 4 per token: 8 tokens 94 against 94 us, 16 tokens 169 against 111)."""
+    return (num_pairs >= 48 or num_pairs >= 2 * min(num_pairs, num_experts)
+            or (num_pairs >= 3 and expert_bytes >= (64 << 20)))
+
+
+def routed_experts(y, x, ids, weights, w_gate_up, w_down, workspace=None, kernel: str = "") -> torch.Tensor:
+    """The experts' outputs added up with the router's weights, by the kernels that suit the step: one or two tokens (and
+    float32, and sizes that are no multiples of 8) read the chosen experts' weights pair by pair; more go through the
+    grouped tcgen05 products (see grouped_experts_preferred).  `workspace` (parts.base.Workspace) lends the scratch;
+    without it the scratch is allocated.  `kernel` = "rows" | "tcgen05" fixes the choice (where the shape allows it)."""
+    T, D = x.shape
+    E, F2, _ = w_gate_up.shape
+    F, top = F2 // 2, ids.shape[1]
+    expert_bytes = 3 * D * F * x.element_size()
+    grouped = kernel == "tcgen05" or (kernel == "" and grouped_experts_preferred(T * top, E, expert_bytes))
+    if grouped and experts_grouped_supported(x.dtype, D, F):
+        R = grouped_rows_tcgen05(T, top, E)
+
+        def buf(name, n, dtype):
+            if workspace is not None:
+                # sized once for the largest step (the address must not move: captured graphs hold it)
+                return workspace.flat(f"{name}_{E}_{top}", grouped_rows_tcgen05(workspace.max_tokens, top, E) * (n // R), dtype)
+            return torch.empty(n, dtype=dtype, device=x.device)
+        slot_of = workspace.rows("moe_slot_of", T, top, torch.int32) if workspace is not None else torch.empty(T * top, dtype=torch.int32, device=x.device)
+        return experts_grouped_tcgen05(y, x, ids, weights, w_gate_up, w_down, buf("moe_tile_expert", R, torch.int32),
+                                       buf("moe_row_token", R, torch.int32), slot_of, buf(f"moe_xs{D}", R * D, x.dtype),
+                                       buf(f"moe_hid{F}", R * F, x.dtype), buf(f"moe_rows{D}", R * D, x.dtype))
     if workspace is not None:
-        offsets = workspace.flat(f"moe_offsets_{E}", E + 1, torch.int32)
+        hid = workspace.rows("moe_hidden", T, top * F, x.dtype)
     else:
-        offsets = torch.empty(E + 1, dtype=torch.int32, device=x.device)
-    return experts_grouped_bf16(y, x, ids, weights, w_gate_up, w_down, offsets, sorted_pairs, slot_of, hid, rows_)
+        hid = torch.empty((T, top * F), dtype=x.dtype, device=x.device)
+    return expert_rows(y, hid, x, ids, weights, w_gate_up, w_down)
 
 
 # ---- projection epilogue: per-head norm, rotary, cache write --------------------------------------------------

@@ -147,6 +147,25 @@ __global__ void gelu_tanh_kernel(T* __restrict__ out, const T* __restrict__ x, i
         out[i] = from_float<T>(gelu_tanh_of(to_float(x[i])));
 }
 
+// bf16, eight elements per thread and step
+__global__ void gelu_tanh_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, int64_t n_chunks) {
+    pdl_trigger();
+    pdl_wait();
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_chunks;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + i * 8);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint4 res;
+        __nv_bfloat162* r = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(h[k]);
+            r[k] = __floats2bfloat162_rn(gelu_tanh_of(f.x), gelu_tanh_of(f.y));
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = res;
+    }
+}
+
 // src row t holds, from column col0 on, `heads` vectors of `width` elements; they land at
 // pages[slot / page_size, head, slot % page_size, :].
 template <typename T>
@@ -205,6 +224,12 @@ extern "C" int cvb_resid_update(float* h, const void* d1, const void* d2, const 
 extern "C" int cvb_gelu_tanh(void* out, const void* x, int64_t n, int dtype, cudaStream_t stream) {
     if (n == 0) return CVB_OK;
     if (n < 0) return CVB_E_SIZE;
+    if (dtype == CVB_DTYPE_BF16 && n % 8 == 0 && ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+        const int64_t chunks = n / 8, want8 = (chunks + 255) / 256;
+        launch_kernel(gelu_tanh_bf16x8_kernel, dim3(static_cast<unsigned>(want8 < 148 * 16 ? want8 : 148 * 16)), dim3(256), 0, stream,
+                      (__nv_bfloat16*)out, (const __nv_bfloat16*)x, chunks);
+        return launch_status();
+    }
     const int64_t want = (n + 255) / 256;
     const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
 #define CALL(TY) launch_kernel(gelu_tanh_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)x, n)

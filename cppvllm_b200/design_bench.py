@@ -1,0 +1,302 @@
+"""Givirax beside Qwen3 at equal layer sizes, random weights, bf16: prefill and decode throughput of whole models through
+the step function, and every kernel of the Givirax parts beside the like kernel of the Qwen3 parts, each with its
+fraction of its own roofline (bytes it must move over the measured copy bandwidth, or flops over the measured bf16 peak).
+
+    python bench.py --design givirax            (or: python -m cppvllm_b200.design_bench)
+
+Sizes: "small" has Qwen3-0.6B's layer sizes (width 1,024, 16 query and 8 kv heads of 128, inner size 3,072), "large"
+Qwen3-8B's (4,096, 32 and 8 heads of 128, 12,288), a few layers each.  The Givirax model of a size has the same width,
+heads and head size, a window of 1,024 positions with 4 kept first tokens, and alternates a dense tanh-GELU feed-forward
+of the same inner size with 8 gated experts, 2 per token, of half that inner size each (the same flops per token as the
+dense gated feed-forward of Qwen3).  Timing: CUDA events around steps that are already warm, buffers rotated or larger
+than the L2 for single kernels.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import shutil
+import sys
+import tempfile
+import time
+
+import torch
+
+SIZES = {
+    "small": dict(width=1024, heads=16, kv_heads=8, dim=128, ff=3072, layers=8, vocab=32000),
+    "large": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=12288, layers=4, vocab=32000),
+}
+WINDOW, KEEP, EXPERTS, TOP = 1024, 4, 8, 2
+
+
+def givirax_config(s, max_positions):
+    mixer = {"dim": s["dim"], "heads": s["heads"], "kv_heads": s["kv_heads"], "vdim": s["dim"], "scale": 1.0 / math.sqrt(s["dim"]),
+             "mask": {"size": WINDOW, "keep_first": KEEP}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["ff"] // 2}, "router": {"experts": EXPERTS, "top": TOP}}
+    layers = [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(s["layers"])]
+    return {"architecture": "Givirax", "vocab": s["vocab"], "width": s["width"], "max_positions": max_positions,
+            "embedding": {"scale": math.sqrt(s["width"])}, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def qwen3_config(s, max_positions):
+    return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=s["width"], num_hidden_layers=s["layers"],
+                num_attention_heads=s["heads"], num_key_value_heads=s["kv_heads"], head_dim=s["dim"], intermediate_size=s["ff"],
+                vocab_size=s["vocab"], rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False,
+                max_position_embeddings=max_positions)
+
+
+def peaks():
+    here = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        with open(os.path.join(here, "MEASURED_PEAKS.json")) as f:
+            j = json.load(f)
+        return {"hbm_gbs": float(j["hbm_gbs"]), "bf16_tflops": float(j["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def model_points(cfg, prefill_tokens, batch, context, steps):
+    """(prefill tokens/s, decode tokens/s at `batch` requests of `context` tokens, decode tokens/s at batch 1)."""
+    from .engine.runner import ModelRunner, StepEntry
+    from .weights.random_init import write_random_model
+    tmp = tempfile.mkdtemp(prefix="cppvllm_b200_design_")
+    try:
+        d = write_random_model(os.path.join(tmp, "m"), cfg, seed=0, std=0.02, norm_spread=0.0)
+        page = 32
+        max_len = max(prefill_tokens, context + 8)
+        r = ModelRunner(d, dtype=torch.bfloat16, page_size=page, num_pages=(batch + 1) * ((max_len + page - 1) // page) + 8,
+                        max_step_tokens=8192, max_seqs=max(batch, 8), max_model_len=max_len)
+        gen = torch.Generator().manual_seed(0)
+        vocab = r.vocab_size
+        best = float("inf")
+        for it in range(4):
+            toks = torch.randint(0, vocab, (prefill_tokens,), generator=gen).tolist()
+            r.cache.admit("p"); r.cache.reserve("p", prefill_tokens)
+            torch.cuda.synchronize()
+            e0, e1 = _events()
+            e0.record()
+            r.step([StepEntry("p", toks, 0, [prefill_tokens - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if it:
+                best = min(best, e0.elapsed_time(e1))
+            r.cache.release("p")
+        out = {"prefill_tok_s": round(prefill_tokens / (best / 1e3), 1), "prefill_ms": round(best, 3)}
+        for b in (batch, 1):
+            ids = [f"d{i}" for i in range(b)]
+            ctx0 = context - steps - 8
+            for i in ids:
+                r.cache.admit(i); r.cache.reserve(i, context + 1)
+            fed, per = 0, max(1, 8192 // b)
+            while fed < ctx0:
+                n = min(per, ctx0 - fed)
+                r.step([StepEntry(i, torch.randint(0, vocab, (n,), generator=gen).tolist(), fed, []) for i in ids])
+                fed += n
+            pos = ctx0
+            e0, e1 = _events()
+            for s in range(8 + steps):
+                if s == 8:
+                    torch.cuda.synchronize()
+                    e0.record()
+                r.step([StepEntry(i, [1 + (s + k) % 100], pos, [0]) for k, i in enumerate(ids)])
+                pos += 1
+            e1.record()
+            torch.cuda.synchronize()
+            ms = e0.elapsed_time(e1) / steps
+            r.check_errors()
+            nbytes = r.model.decode_weight_bytes() + sum(
+                b * min(context, (cs.window + cs.keep_first) if cs.window else context) * cs.elements_per_token() * 2 * len(m)
+                for cs, m in r.group_specs)
+            out[f"decode_b{b}_tok_s"] = round(b / (ms / 1e3), 1)
+            out[f"decode_b{b}_ms"] = round(ms, 4)
+            out[f"decode_b{b}_hbm_frac"] = round(nbytes / (ms / 1e3) / 1e9 / peaks()["hbm_gbs"], 4)
+            for i in ids:
+                r.cache.release(i)
+        del r
+        torch.cuda.empty_cache()
+        return out
+    finally:
+        shutil.rmtree(tmp, ignore_errors=True)
+
+
+# ---- single kernels, in pairs ------------------------------------------------------------------------------------------
+
+def _us(fn, iters=20):
+    from .kernel_bench import _time
+    return _time(fn, iters)
+
+
+def kernel_pairs(s, pk):
+    """Each kernel of the Givirax parts beside the like kernel of the Qwen3 parts at the same sizes: microseconds and the
+    fraction of its roofline, and how much further from its roofline the new one is (`gap`, 1 = equally far)."""
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bf = torch.bfloat16
+    D, H, KV, hd, I = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    F = I // 2
+    page, out = 32, {}
+
+    def rnd(*shape, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=d, dtype=torch.float32) * scale).to(bf)
+
+    def pair(name, new_us, new_work, like_us, like_work, unit):
+        peak = pk["hbm_gbs"] * 1e9 if unit == "bytes" else pk["bf16_tflops"] * 1e12
+        fn, fl = new_work / (new_us * 1e-6) / peak, like_work / (like_us * 1e-6) / peak
+        out[name] = {"new_us": round(new_us, 2), "new_frac": round(fn, 4), "like_us": round(like_us, 2), "like_frac": round(fl, 4),
+                     "gap": round(fl / fn, 2), "roofline": "copy bandwidth" if unit == "bytes" else "bf16 peak"}
+
+    # -- attention of a prompt of 2,048 tokens behind the window ---------------------------------------------------------
+    T = 2048
+    n_pages = T // page
+    visible = sum(min(p + 1, WINDOW) + (min(KEEP, max(0, p - WINDOW + 1))) for p in range(T))
+    flops = 4.0 * H * hd * visible
+    tables = torch.arange(n_pages, dtype=torch.int32, device=d).view(1, n_pages)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=d)
+    pos = torch.arange(T, dtype=torch.int32, device=d)
+    keys_pages = rnd(n_pages + 1, KV, page, hd)
+    qk = rnd(T, (H + KV) * hd)
+    att = torch.empty(T, H * hd, dtype=bf, device=d)
+    scale = 1 / math.sqrt(hd)
+    tiles = ops.attn_keys_tiles([T], H, KV)
+    new = _us(lambda i: ops.attn_keys_bf16(att, qk, keys_pages, tables, cu, pos, 1, tiles, H, KV, hd, page, scale, WINDOW, KEEP))
+    kv_pages = rnd(n_pages + 1, 2, KV, page, hd)
+    q = rnd(T, H * hd)
+    tiles_tc = ops.prefill_tiles_tcgen05([T], H, KV)
+    like = _us(lambda i: ops.attn_prefill_tcgen05(att, q, kv_pages, tables, cu, pos, 1, tiles_tc, H, KV, hd, page, scale, window=WINDOW))
+    flops_like = 4.0 * H * hd * sum(min(p + 1, WINDOW) for p in range(T))
+    pair("attention_prefill_2048", new, flops, like, flops_like, "flops")
+
+    # -- attention of decoded tokens: batch 8 at 4,096 tokens, a window of 1,024 ------------------------------------------
+    B, ctx = 8, 4096
+    pps = ctx // page
+    copies = 8
+    tabs = [torch.randperm(B * pps, generator=g, device=d).to(torch.int32).view(B, pps).contiguous() for _ in range(copies)]
+    keys_big = [rnd(B * pps + 1, KV, page, hd) for _ in range(copies)]
+    kv_big = [rnd(B * pps + 1, 2, KV, page, hd) for _ in range(copies)]
+    cu_b = torch.arange(0, B + 1, dtype=torch.int32, device=d)
+    pos_b = torch.full((B,), ctx - 1, dtype=torch.int32, device=d)
+    qk_b, q_b = rnd(B, (H + KV) * hd), rnd(B, H * hd)
+    att_b = torch.empty(B, H * hd, dtype=bf, device=d)
+    new = _us(lambda i: ops.attn_keys_bf16(att_b, qk_b, keys_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, page,
+                                           scale, WINDOW, KEEP, all_single=True))
+    splits = 4
+    scratch = torch.empty(max(1, ops.attn_decode_scratch_floats(B, KV, hd, splits)), dtype=torch.float32, device=d)
+    like = _us(lambda i: ops.attn_decode_bf16(att_b, q_b, kv_big[i % copies], tabs[i % copies], cu_b, pos_b, B, H, KV, hd, page, scale,
+                                              splits, scratch, window=WINDOW))
+    pair("attention_decode_b8_window_1024", new, B * (WINDOW + KEEP) * KV * hd * 2.0, like, B * WINDOW * KV * hd * 4.0, "bytes")
+    del keys_big, kv_big
+
+    # -- the feed-forward of 2,048 tokens: grouped experts beside the dense gated product ---------------------------------
+    x = rnd(T, D)
+    w_router = torch.randn(EXPERTS, D, generator=g, device=d)
+    b_router = torch.zeros(EXPERTS, device=d)
+    ids = torch.empty(T, TOP, dtype=torch.int32, device=d)
+    wts = torch.empty(T, TOP, dtype=torch.float32, device=d)
+    ops.route_topk(ids, wts, x, w_router, b_router)
+    wgu, wd = rnd(EXPERTS, 2 * F, D, scale=0.02), rnd(EXPERTS, D, F, scale=0.02)
+    y = torch.empty(T, D, dtype=bf, device=d)
+    R = ops.grouped_rows_tcgen05(T, TOP, EXPERTS)
+    scr2 = dict(tile_expert=torch.empty(R, dtype=torch.int32, device=d), row_token=torch.empty(R, dtype=torch.int32, device=d),
+                slot_of=torch.empty(T * TOP, dtype=torch.int32, device=d), xs=torch.empty(R, D, dtype=bf, device=d), hid=torch.empty(R, F, dtype=bf, device=d),
+                rows=torch.empty(R, D, dtype=bf, device=d))
+    new = _us(lambda i: ops.experts_grouped_tcgen05(y, x, ids, wts, wgu, wd, **scr2))
+    w_gate_up, w_down = rnd(2 * I, D, scale=0.02), rnd(D, I, scale=0.02)
+    act = torch.empty(T, I, dtype=bf, device=d)
+    gu = torch.empty(T, 2 * I, dtype=bf, device=d)
+
+    def dense(i):
+        if ops.gated_product_fused(bf, w_gate_up, T):
+            ops.gemm_bf16_tcgen05(act, x, w_gate_up, swiglu=True)
+        else:
+            ops.linear(x, w_gate_up, out=gu)
+            ops.swiglu(act, gu)
+        ops.linear(act, w_down, out=y)
+    like = _us(dense)
+    pair("feed_forward_2048_tokens", new, 2.0 * T * TOP * 3 * D * F, like, 2.0 * T * 3 * D * I, "flops")
+    new = _us(lambda i: ops.route_topk(ids, wts, x, w_router, b_router))
+    out["router_2048_tokens"] = {"new_us": round(new, 2), "note": "no like kernel in the closest model"}
+
+    # -- the feed-forward of 8 decoded tokens --------------------------------------------------------------------------------
+    copies = max(2, int(300e6 // (wgu.numel() * 2 + wd.numel() * 2)) + 1)
+    wgus, wds = [wgu] + [rnd(EXPERTS, 2 * F, D, scale=0.02) for _ in range(copies - 1)], [wd] + [rnd(EXPERTS, D, F, scale=0.02) for _ in range(copies - 1)]
+    x8, y8 = x[:8].contiguous(), torch.empty(8, D, dtype=bf, device=d)
+    ids8, wts8 = ids[:8].contiguous(), wts[:8].contiguous()
+    hid8 = torch.empty(8 * TOP, F, dtype=bf, device=d)
+    rows_us = _us(lambda i: ops.expert_rows(y8, hid8, x8, ids8, wts8, wgus[i % copies], wds[i % copies]))
+    from .parts.base import Workspace
+    ws8 = Workspace(d, 8)
+    new = _us(lambda i: ops.routed_experts(y8, x8, ids8, wts8, wgus[i % copies], wds[i % copies], workspace=ws8))
+    used = len(set(ids8.flatten().tolist()))
+    dense_copies = max(2, int(300e6 // (w_gate_up.numel() * 2 + w_down.numel() * 2)) + 1)
+    wgs = [w_gate_up] + [rnd(2 * I, D, scale=0.02) for _ in range(dense_copies - 1)]
+    wdn = [w_down] + [rnd(D, I, scale=0.02) for _ in range(dense_copies - 1)]
+    act8, gu8 = torch.empty(8, I, dtype=bf, device=d), torch.empty(8, 2 * I, dtype=bf, device=d)
+
+    def dense8(i):
+        ops.project_rows(x8, wgs[i % dense_copies], gu8, 8)
+        ops.swiglu(act8, gu8)
+        ops.project_rows(act8, wdn[i % dense_copies], y8, 8)
+    dense8(0)
+    like = _us(dense8)
+    pair("feed_forward_8_decoded_tokens", new, used * 3.0 * D * F * 2, like, 3.0 * D * I * 2, "bytes")
+    out["feed_forward_8_decoded_tokens"]["pair_by_pair_us"] = round(rows_us, 2)
+    out["feed_forward_8_decoded_tokens"]["experts_in_use"] = used
+    del wgus, wds, wgs, wdn
+
+    # -- the residual update with its norm, and the activation, 2,048 tokens ---------------------------------------------------
+    h32 = torch.randn(T, D, generator=g, device=d)
+    d1, d2, normed = rnd(T, D), rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
+    w = torch.ones(D, device=d)
+    new = _us(lambda i: ops.resid_update(h32, (d1, d2), norm_weight=w, eps=1e-5, out=normed))
+    h16 = rnd(T, D)
+    like = _us(lambda i: ops.add_rmsnorm(normed, h16, d1, w, 1e-6))
+    pair("residual_add_and_norm_2048_tokens", new, T * D * (4 + 4 + 2 + 2 + 2.0), like, T * D * (2 + 2 + 2 + 2.0), "bytes")
+    up = rnd(T, I)
+    new = _us(lambda i: ops.gelu_tanh(up, up))
+    gu_t = rnd(T, 2 * I)
+    like = _us(lambda i: ops.swiglu(act, gu_t))
+    pair("activation_2048_tokens", new, T * I * 4.0, like, T * I * 6.0, "bytes")
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(prog="design_bench", description=__doc__.split("\n\n")[0])
+    ap.add_argument("--design", default="givirax", choices=["givirax"])
+    ap.add_argument("--sizes", default="small,large")
+    ap.add_argument("--steps", type=int, default=48)
+    ap.add_argument("--no-kernels", action="store_true", help="whole models only")
+    ap.add_argument("--no-models", action="store_true", help="single kernels only")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        print("design_bench: needs a CUDA device", file=sys.stderr)
+        return 2
+    from .csrc import ops
+    ops.configure_library_matmul()
+    pk = peaks()
+    result = {"design": a.design, "closest": "Qwen3ForCausalLM", "dtype": "bf16", "data": "synthetic, random weights", "peaks": pk,
+              "window": WINDOW, "keep_first": KEEP, "experts": EXPERTS, "top": TOP, "sizes": {}}
+    for name in a.sizes.split(","):
+        s = SIZES[name]
+        entry = {"shape": s}
+        if not a.no_models:
+            t0 = time.time()
+            entry["givirax"] = model_points(givirax_config(s, 4160), 2048, 8, 4096, a.steps)
+            entry["qwen3"] = model_points(qwen3_config(s, 4160), 2048, 8, 4096, a.steps)
+            entry["seconds"] = round(time.time() - t0, 1)
+        if not a.no_kernels:
+            entry["kernels"] = kernel_pairs(s, pk)
+        result["sizes"][name] = entry
+    print(json.dumps(result))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -84,7 +84,7 @@ class KeysAttention(Mixer):
             q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * ctx.num_seqs
             ops.attn_keys_bf16(att, qk, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
                                ops.attn_keys_tiles(q_lens, H, KV), H, KV, hd, g.page_size, self.scale, window=self.window,
-                               keep_first=self.keep_first)
+                               keep_first=self.keep_first, all_single=ctx.all_decode and ctx.num_tokens == ctx.num_seqs)
             return
         ops.paged_attention_general(att, qk, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions, self.num_heads,
                                     self.num_kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,

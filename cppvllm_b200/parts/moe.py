@@ -5,9 +5,10 @@
   the ``top`` experts with the largest logits, weighted by the softmax over the chosen logits only; an expert is
   Wdown (silu(Wgate x) * (Wup x)) without biases; the output is the weighted sum of the chosen experts' outputs.  Expert e's
   tensors are ``<prefix>e<e>.gate|up|down``; they are stacked at load time into [E, 2 ff, D] (gate rows over up rows) and
-  [E, D, ff], so that a kernel reaches every expert from one base address.  A few tokens read only their chosen experts'
-  weights (two kernels spread over all SMs); many tokens are sorted by expert on the device and go through two grouped
-  products on the tensor cores (csrc/moe.cu); nothing travels to the host, so steps stay capturable.
+  [E, D, ff], so that a kernel reaches every expert from one base address.  One or two tokens read only their chosen
+  experts' weights pair by pair (two kernels spread over all SMs); more are sorted by expert on the device and go through
+  two grouped products on the tcgen05 kernel (csrc/moe.cu, csrc/gemm_tcgen05.cu); nothing travels to the host, so steps
+  stay capturable.
 """
 from __future__ import annotations
 
@@ -97,4 +98,4 @@ class RoutedGLU(FeedForward):
         ops.route_topk(ids, weights, x, self.w_router, self.b_router)
         y = ws.rows("ffn_out", T, self.hidden_size, x.dtype)
         return ops.routed_experts(y, x, ids, weights, self.w_gate_up, self.w_down, workspace=ws,
-                                  grouped=False if self.rt.plain_kernels else None)
+                                  kernel="rows" if self.rt.plain_kernels else "")

@@ -114,7 +114,8 @@ def test_router_chooses_the_largest_logits_and_weights_them_by_their_own_softmax
 
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,D,F,T", [(5, 2, 48, 24, 9), (3, 3, 50, 12, 4), (8, 2, 128, 64, 300), (4, 1, 64, 40, 70)])
+@pytest.mark.parametrize("E,top,D,F,T", [(5, 2, 48, 24, 9), (3, 3, 50, 12, 4), (8, 2, 128, 64, 300), (4, 1, 64, 40, 70), (6, 2, 256, 136, 700),
+                                         (16, 3, 64, 8, 130)])
 def test_experts_against_plain_arithmetic(ops, dt, E, top, D, F, T):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(T, D, generator=g).to(dt)
@@ -128,10 +129,13 @@ def test_experts_against_plain_arithmetic(ops, dt, E, top, D, F, T):
             e = int(ids[t, k])
             gate, up = wgu[e, :F].double() @ x[t].double(), wgu[e, F:].double() @ x[t].double()
             ref[t] += wts[t, k].double() * (wd[e].double() @ (gate * torch.sigmoid(gate) * up))
-    y = torch.empty(T, D, dtype=dt, device=dev())
-    ops.routed_experts(y, x.to(dev()), ids.to(dev()), wts.to(dev()), wgu.to(dev()), wd.to(dev()))
     tol = 2e-5 if dt == torch.float32 else 3e-2
-    assert float((y.cpu().double() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max()))
+    kernels = ["", "rows"] + (["tcgen05"] if dt == torch.bfloat16 and D % 8 == 0 and F % 8 == 0 else [])
+    for kernel in kernels:                                   # every path gives the same sums, to rounding
+        y = torch.full((T, D), float("nan"), dtype=dt, device=dev())
+        ops.routed_experts(y, x.to(dev()), ids.to(dev()), wts.to(dev()), wgu.to(dev()), wd.to(dev()), kernel=kernel)
+        ops.check_device_errors(dev())
+        assert float((y.cpu().double() - ref).abs().max()) <= tol * max(1.0, float(ref.abs().max())), kernel
 
 
 def paged_keys(keys, page, order_seed):
