@@ -31,6 +31,7 @@ struct KeysAttnParams {
     const int* cu_seqlens;              // [S + 1]
     const int* positions;               // [T]
     int q_stride, table_width, S, H, KV, page_size, window, keep_first, num_pages;
+    int page_shift;                     // log2(page_size) if that is a power of two, else -1
     float scale_log2;                   // scale * log2(e)
     int* err;
 };
@@ -48,13 +49,18 @@ __device__ __forceinline__ void mma_16816(float (&d)[4], const uint32_t (&a)[4],
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// page and offset of key j
+__device__ __forceinline__ void page_of(const KeysAttnParams& p, int j, int& slot, int& off) {
+    if (p.page_shift >= 0) { slot = j >> p.page_shift; off = j & (p.page_size - 1); }
+    else { slot = j / p.page_size; off = j - slot * p.page_size; }
+}
 __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int HD>
-__global__ void __launch_bounds__(kKeysThreads)
+__global__ void __launch_bounds__(kKeysThreads, 3)
 attn_keys_kernel(const KeysAttnParams p) {
     pdl_trigger();
     pdl_wait();
@@ -110,13 +116,14 @@ attn_keys_kernel(const KeysAttnParams p) {
             bool need = j <= key_hi && (j >= key_lo || j < keep);
             const __nv_bfloat16* src = p.pages;
             if (need) {
-                const int slot = j / p.page_size;
+                int slot, off;
+                page_of(p, j, slot, off);
                 if (slot != last_slot) { page = slot < p.table_width ? table[slot] : -1; last_slot = slot; }
                 if (page < 0 || page >= p.num_pages) {
                     atomicExch(p.err, 4);                 // a key a token of this block must see has no page
                     need = false;
                 } else {
-                    src = p.pages + ((static_cast<int64_t>(page) * p.KV + kvh) * p.page_size + (j - slot * p.page_size)) * HD + c * 8;
+                    src = p.pages + ((static_cast<int64_t>(page) * p.KV + kvh) * p.page_size + off) * HD + c * 8;
                 }
             }
             cp_async16(dst + r * LD + c * 8, src, need);
@@ -301,19 +308,26 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
         const int key0 = (it < n_kept ? it : first_tile + it - n_kept) * kDecKeys;
         __nv_bfloat16* dst = my + stage * kDecKeys * LD;
         int last_slot = -1, page = -1;
+        const __nv_bfloat16* page_base = p.pages;
+        // a lane's chunks: with 32 % CPR == 0 the lane keeps its column and walks down the rows
         for (int i = lane; i < kDecKeys * CPR; i += 32) {
             const int r = i / CPR, c = i - r * CPR;
             const int j = key0 + r;
             bool need = j <= pos && (j >= key_lo || j < keep);
             const __nv_bfloat16* src = p.pages;
             if (need) {
-                const int slot = j / p.page_size;
-                if (slot != last_slot) { page = slot < p.table_width ? table[slot] : -1; last_slot = slot; }
+                int slot, off;
+                page_of(p, j, slot, off);
+                if (slot != last_slot) {
+                    page = slot < p.table_width ? table[slot] : -1;
+                    last_slot = slot;
+                    page_base = p.pages + (static_cast<int64_t>(page) * p.KV + kvh) * p.page_size * HD;
+                }
                 if (page < 0 || page >= p.num_pages) {
                     atomicExch(p.err, 4);
                     need = false;
                 } else {
-                    src = p.pages + ((static_cast<int64_t>(page) * p.KV + kvh) * p.page_size + (j - slot * p.page_size)) * HD + c * 8;
+                    src = page_base + off * HD + c * 8;
                 }
             }
             cp_async16(dst + r * LD + c * 8, src, need);
@@ -500,6 +514,9 @@ extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const 
     p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
     p.q_stride = q_stride; p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size;
     p.window = window; p.keep_first = keep_first; p.num_pages = num_pages;
+    p.page_shift = -1;
+    for (int sh = 0; sh < 31; ++sh)
+        if ((1 << sh) == page_size) p.page_shift = sh;
     p.scale_log2 = scale * kLog2eKeys;
     p.err = err_flag;
     if (all_single && H / KV <= 16) {                     // every request brings one token: the kernel for decoded tokens
