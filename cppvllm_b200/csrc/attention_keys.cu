@@ -32,6 +32,10 @@ struct KeysAttnParams {
     const int* positions;               // [T]
     int q_stride, table_width, S, H, KV, page_size, window, keep_first, num_pages;
     int page_shift;                     // log2(page_size) if that is a power of two, else -1
+    // decode form only: the key tiles of a (request, kv head) are shared out among `splits` blocks (gridDim.z); with more
+    // than one, a block leaves its part (unnormalised rows, maxima, sums) in `parts` and a second kernel merges them
+    int splits;
+    float* parts;                       // [S, KV, splits, 16, HD + 2]
     float scale_log2;                   // scale * log2(e)
     int* err;
 };
@@ -266,7 +270,8 @@ attn_keys_kernel(const KeysAttnParams p) {
 // warps have nothing to share but the keys, and each takes every eighth key tile (32 keys) for itself: it fetches its tiles
 // into two stages of its own (cp.async by its own lanes, __syncwarp, no block-wide barrier in the loop), keeps its own
 // running maximum, sum and accumulator, and the eight partial results are merged through shared memory at the end.  Up to
-// sixteen tiles are in flight per block.  Eight warps of short tiles rather than four of long ones: with one warp per
+// sixteen tiles are in flight per block.  When few (request, kv head) pairs would leave SMs idle, the tiles are shared out
+// among `splits` blocks as well, which leave their parts in scratch for a small merge kernel.  Eight warps of short tiles rather than four of long ones: with one warp per
 // scheduler every instruction's latency shows (measured: 14 k instructions a warp in 90 k cycles, stalled on fixed-latency
 // dependencies), two warps per scheduler with half the instructions each overlap.
 constexpr int kDecWarps = 8;
@@ -334,8 +339,10 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
         }
     };
 
-    const int my_tiles = (n_tiles - warp + kDecWarps - 1) / kDecWarps;     // tiles warp, warp + 4, ...
-    if (my_tiles > 0) load_tile(warp, 0);
+    const int lanes_w = kDecWarps * p.splits;             // warps that share the tiles: this block's and its siblings'
+    const int gw = blockIdx.z * kDecWarps + warp;
+    const int my_tiles = n_tiles > gw ? (n_tiles - gw + lanes_w - 1) / lanes_w : 0;     // tiles gw, gw + lanes_w, ...
+    if (my_tiles > 0) load_tile(gw, 0);
     cp_async_commit();
     cp_async_wait<1>();                                   // this thread's share of the queries
     __syncthreads();                                      // everybody's share
@@ -349,8 +356,8 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     for (int n = 0; n < my_tiles; ++n) {
-        const int it = warp + n * kDecWarps;
-        if (n + 1 < my_tiles) load_tile(it + kDecWarps, (n + 1) & 1);
+        const int it = gw + n * lanes_w;
+        if (n + 1 < my_tiles) load_tile(it + lanes_w, (n + 1) & 1);
         cp_async_commit();
         cp_async_wait<1>();
         __syncwarp();
@@ -425,7 +432,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
     }
     cp_async_wait<0>();
 
-    // merge the four warps' parts: each leaves its sums, maxima and its accumulator [16][HD] (float) in its own stages
+    // merge the warps' parts: each leaves its sums, maxima and its accumulator [16][HD] (float) in its own stages
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         l[half] += __shfl_xor_sync(0xffffffffu, l[half], 1);
@@ -458,6 +465,36 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
             ll += red_ml[(w * 16 + r) * 2 + 1] * f;
             acc += reinterpret_cast<const float*>(sK + w * 2 * kDecKeys * LD)[r * HD + d] * f;
         }
+        if (p.splits == 1) {
+            p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        } else {
+            float* dst = p.parts + ((static_cast<int64_t>(seq) * p.KV + kvh) * p.splits + blockIdx.z) * 16 * (HD + 2) + r * (HD + 2);
+            dst[d] = acc;
+            if (d == 0) { dst[HD] = mm; dst[HD + 1] = ll; }
+        }
+    }
+}
+
+// out = the parts of a (request, kv head) added up: rows scaled to the common maximum, divided by the common sum
+template <int HD>
+__global__ void attn_keys_merge_kernel(const KeysAttnParams p) {
+    pdl_trigger();
+    pdl_wait();
+    const int g = p.H / p.KV;
+    const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int t = p.cu_seqlens[seq];
+    const float* base = p.parts + (static_cast<int64_t>(seq) * p.KV + kvh) * p.splits * 16 * (HD + 2);
+    for (int i = threadIdx.x; i < g * HD; i += blockDim.x) {
+        const int r = i / HD, d = i - r * HD;
+        float mm = -INFINITY;
+        for (int z = 0; z < p.splits; ++z) mm = fmaxf(mm, base[(z * 16 + r) * (HD + 2) + HD]);
+        float ll = 0.f, acc = 0.f;
+        for (int z = 0; z < p.splits; ++z) {
+            const float* row = base + (z * 16 + r) * (HD + 2);
+            const float f = row[HD] == -INFINITY ? 0.f : ex2(row[HD] - mm);
+            ll += row[HD + 1] * f;
+            acc += row[d] * f;
+        }
         p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
     }
 }
@@ -471,7 +508,8 @@ int launch_attn_keys_decode(const KeysAttnParams& p, cudaStream_t stream) {
             return launch_status();
         raised = true;
     }
-    launch_kernel(attn_keys_decode_kernel<HD>, dim3(p.S, p.KV), dim3(kDecWarps * 32), smem, stream, p);
+    launch_kernel(attn_keys_decode_kernel<HD>, dim3(p.S, p.KV, p.splits), dim3(kDecWarps * 32), smem, stream, p);
+    if (p.splits > 1) launch_kernel(attn_keys_merge_kernel<HD>, dim3(p.S, p.KV), dim3(128), 0, stream, p);
     return launch_status();
 }
 
@@ -500,7 +538,8 @@ extern "C" int cvb_attn_keys_supported(int H, int KV, int hd) {
 extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const void* pages, const int* block_tables,
                                   int table_width, const int* cu_seqlens, const int* positions, int S, int num_tiles, int H,
                                   int KV, int hd, int page_size, int window, int keep_first, float scale, int num_pages,
-                                  int all_single, int* err_flag, cudaStream_t stream) {
+                                  int all_single, int splits, float* parts, int64_t parts_floats, int* err_flag,
+                                  cudaStream_t stream) {
     if (num_tiles == 0 || S == 0) return CVB_OK;
     if (S < 0 || num_tiles < 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || window < 0 || keep_first < 0) return CVB_E_SIZE;
     if (!cvb_attn_keys_supported(H, KV, hd)) return CVB_E_UNSUPPORTED;
@@ -519,6 +558,12 @@ extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const 
         if ((1 << sh) == page_size) p.page_shift = sh;
     p.scale_log2 = scale * kLog2eKeys;
     p.err = err_flag;
+    p.splits = 1; p.parts = nullptr;
+    if (all_single && H / KV <= 16 && splits > 1) {
+        if (splits > 64) return CVB_E_SIZE;
+        if (parts == nullptr || parts_floats < static_cast<int64_t>(S) * KV * splits * 16 * (hd + 2)) return CVB_E_SCRATCH;
+        p.splits = splits; p.parts = parts;
+    }
     if (all_single && H / KV <= 16) {                     // every request brings one token: the kernel for decoded tokens
         switch (hd) {
             case 16: return launch_attn_keys_decode<16>(p, stream);

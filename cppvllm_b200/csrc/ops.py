@@ -313,6 +313,21 @@ def attn_keys_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, h
             and num_kv_heads > 0 and num_heads % num_kv_heads == 0 and num_heads // num_kv_heads <= 64)
 
 
+def attn_keys_scratch_floats(num_seqs: int, num_kv_heads: int, head_dim: int, splits: int) -> int:
+    return num_seqs * num_kv_heads * splits * 16 * (head_dim + 2)
+
+
+def attn_keys_decode_splits(num_seqs: int, num_kv_heads: int, visible_keys: int, sms: int = 148) -> int:
+    """Blocks per (request, kv head) of a decode step: enough to give every SM a block while a warp keeps a tile of 32 keys
+    or more (eight warps per block), at most 8."""
+    pairs = max(1, num_seqs * num_kv_heads)
+    tiles = max(1, (visible_keys + 31) // 32)
+    splits = 1
+    while splits < 8 and pairs * splits * 2 <= 2 * sms and tiles >= 8 * splits * 2:
+        splits *= 2
+    return splits
+
+
 def attn_keys_tiles(q_lens, num_heads: int, num_kv_heads: int) -> int:
     """Blocks per kv head: per request ceil(tokens / (64 // group))."""
     tpt = 64 // (num_heads // num_kv_heads)
@@ -321,22 +336,27 @@ def attn_keys_tiles(q_lens, num_heads: int, num_kv_heads: int) -> int:
 
 def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
                    positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int,
-                   page_size: int, scale: float, window: int = 0, keep_first: int = 0, all_single: bool = False) -> torch.Tensor:
+                   page_size: int, scale: float, window: int = 0, keep_first: int = 0, all_single: bool = False, splits: int = 1,
+                   scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Attention of prompt portions and decoded tokens over pages [kv head, slot, head_dim] whose keys are also the
     values; `q` may be the packed output of a projection (rows of q.shape[1] elements, queries first).  `all_single`:
     every request brings exactly one token (a decode step): a block per (request, kv head) whose warps share out the key
-    tiles among themselves."""
+    tiles among themselves; with `splits` > 1 that many blocks share them, through `scratch` (float32,
+    attn_keys_scratch_floats elements) and a merge kernel."""
     _cuda(out, q, pages, block_tables, cu_seqlens, positions); _contig(out, q, pages, block_tables, cu_seqlens, positions)
     if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_keys_bf16 takes bf16 queries, pages and output")
     if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or cu_seqlens.dtype != torch.int32 or positions.dtype != torch.int32:
         raise KernelError("attn_keys_bf16: block_tables [S, W], cu_seqlens and positions must be int32")
     num_pages = pages.numel() // (num_kv_heads * page_size * head_dim)
+    if splits > 1 and (scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or not scratch.is_contiguous()):
+        raise KernelError("attn_keys_bf16: splits need a contiguous float32 CUDA scratch")
     _check(_attn_keys_lib().cvb_attn_keys_bf16(
         _ptr(out), _ptr(q), c_int(q.shape[1]), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), c_int(num_pages), c_int(1 if all_single else 0),
-        _ptr(error_flag(q.device)), _stream()), "attn_keys_bf16")
+        c_int(splits), _ptr(scratch), c_int64(scratch.numel() if scratch is not None else 0),
+        _ptr(error_flag(q.device)), _stream()), "attn_keys_bf16", kernels=2 if all_single and splits > 1 else 1)
     return out
 
 

@@ -185,8 +185,10 @@ def kernel_pairs(s, pk):
     pos_b = torch.full((B,), ctx - 1, dtype=torch.int32, device=d)
     qk_b, q_b = rnd(B, (H + KV) * hd), rnd(B, H * hd)
     att_b = torch.empty(B, H * hd, dtype=bf, device=d)
+    z = ops.attn_keys_decode_splits(B, KV, WINDOW + KEEP)
+    parts = torch.empty(ops.attn_keys_scratch_floats(B, KV, hd, z), dtype=torch.float32, device=d)
     new = _us(lambda i: ops.attn_keys_bf16(att_b, qk_b, keys_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, KV, hd, page,
-                                           scale, WINDOW, KEEP, all_single=True))
+                                           scale, WINDOW, KEEP, all_single=True, splits=z, scratch=parts))
     splits = 4
     scratch = torch.empty(max(1, ops.attn_decode_scratch_floats(B, KV, hd, splits)), dtype=torch.float32, device=d)
     like = _us(lambda i: ops.attn_decode_bf16(att_b, q_b, kv_big[i % copies], tabs[i % copies], cu_b, pos_b, B, H, KV, hd, page, scale,

@@ -82,9 +82,17 @@ class KeysAttention(Mixer):
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         if not self.force_general and ops.attn_keys_supported(qk.dtype, H, KV, hd, qk.shape[1]):
             q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * ctx.num_seqs
+            single = ctx.all_decode and ctx.num_tokens == ctx.num_seqs
+            splits, scratch = 1, None
+            if single:
+                visible = min(ctx.max_kv_len, self.window + self.keep_first) if self.window > 0 else ctx.max_kv_len
+                splits = ops.attn_keys_decode_splits(ctx.num_seqs, KV, visible)
+                if splits > 1:
+                    most = ops.attn_keys_scratch_floats(self.rt.workspace.max_seqs, KV, hd, 8)
+                    scratch = self.rt.workspace.flat(f"attn_keys_parts_{KV}_{hd}", most, torch.float32)
             ops.attn_keys_bf16(att, qk, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
                                ops.attn_keys_tiles(q_lens, H, KV), H, KV, hd, g.page_size, self.scale, window=self.window,
-                               keep_first=self.keep_first, all_single=ctx.all_decode and ctx.num_tokens == ctx.num_seqs)
+                               keep_first=self.keep_first, all_single=single, splits=splits, scratch=scratch)
             return
         ops.paged_attention_general(att, qk, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions, self.num_heads,
                                     self.num_kv_heads, self.head_dim, g.page_size, self.scale, window=self.window,

@@ -161,7 +161,7 @@ def attention_plain(q, keys, positions, H, KV, hd, scale, window, keep):
     return out
 
 
-def run_both(ops, q, keys, positions_by_seq, H, KV, hd, page, scale, window, keep, dt, tensor_cores):
+def run_both(ops, q, keys, positions_by_seq, H, KV, hd, page, scale, window, keep, dt, tensor_cores, splits=0):
     """q [T, H, hd]; one request per entry of positions_by_seq (consecutive positions), all reading the same keys."""
     pages, table = paged_keys(keys.to(dt), page, 7)
     S = len(positions_by_seq)
@@ -182,8 +182,10 @@ def run_both(ops, q, keys, positions_by_seq, H, KV, hd, page, scale, window, kee
     pos_t = torch.tensor(positions, dtype=torch.int32, device=dev())
     if tensor_cores:
         q_lens = [len(x) for x in positions_by_seq]
+        scratch = torch.full((ops.attn_keys_scratch_floats(S, KV, hd, max(1, splits)),), float("nan"), device=dev()) if splits > 1 else None
         ops.attn_keys_bf16(out, packed, pages.to(dev()), tables.to(dev()), cu.to(dev()), pos_t, S, ops.attn_keys_tiles(q_lens, H, KV),
-                           H, KV, hd, page, scale, window=window, keep_first=keep)
+                           H, KV, hd, page, scale, window=window, keep_first=keep, all_single=splits > 0, splits=max(1, splits),
+                           scratch=scratch)
     else:
         ops.paged_attention_general(out, packed, pages.to(dev()), tables.to(dev()), seq_of.to(dev()), pos_t, H, KV, hd, page, scale,
                                     window=window, num_tokens=T, keep_first=keep, keys_are_values=True)
@@ -216,6 +218,25 @@ def test_attention_over_keys_random(ops, H, KV, hd, page, window, keep, tensor_c
     ref = attention_plain(q, keys, positions, H, KV, hd, scale, window, keep)
     tol = 1e-5 if dt == torch.float32 else 2e-2
     assert float((got.double() - ref).abs().max()) <= tol * float(ref.abs().max())
+
+
+@pytest.mark.parametrize("splits", [1, 2, 8])
+@pytest.mark.parametrize("H,KV,hd,page,window,keep", CASES)
+def test_attention_of_decoded_tokens_alone(ops, H, KV, hd, page, window, keep, splits):
+    """The form for steps in which every request brings one token: positions at the start of a sequence, around the
+    window's and the kept tokens' edges, at tile and page borders and far out; one block per (request, kv head) and the
+    tiles shared out among 2 and 8 blocks."""
+    g = torch.Generator().manual_seed(hd * 3 + window)
+    n = 700
+    keys = torch.randn(n, KV, hd, generator=g).to(torch.bfloat16).float()
+    ps = sorted({0, 1, 2, keep, max(0, keep - 1), 31, 32, 33, 63, 64, 65, window, max(0, window - 1), window + 1, window + keep,
+                 255, 256, 300, 511, 699} & set(range(n)))
+    seqs = [[p] for p in ps]
+    q = torch.randn(len(ps), H, hd, generator=g).to(torch.bfloat16).float()
+    scale = 0.9 / math.sqrt(hd)
+    got, positions = run_both(ops, q, keys, seqs, H, KV, hd, page, scale, window, keep, torch.bfloat16, True, splits=splits)
+    ref = attention_plain(q, keys, positions, H, KV, hd, scale, window, keep)
+    assert float((got.double() - ref).abs().max()) <= 2e-2 * float(ref.abs().max())
 
 
 @pytest.mark.parametrize("tensor_cores", [False, True])
@@ -251,7 +272,8 @@ def test_a_key_that_stands_out_shows_every_edge(ops, H, KV, hd, page, window, ke
                 q[t, h] = k2[j, h // (H // KV)] * 1.5             # score 54 against the marked key, about 0 elsewhere
             if dt == torch.bfloat16:
                 q = q.to(dt).float()
-            got, positions = run_both(ops, q, k2, seqs, H, KV, hd, page, scale, window, keep, dt, tensor_cores)
+            got, positions = run_both(ops, q, k2, seqs, H, KV, hd, page, scale, window, keep, dt, tensor_cores,
+                                      splits=2 if tensor_cores and len(seqs[0]) == 1 else 0)
             assert positions[t] == p
             for h in range(H):
                 target = k2[j, h // (H // KV)]
