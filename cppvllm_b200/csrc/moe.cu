@@ -1,7 +1,7 @@
 // Routed feed-forward (mixture of experts): the router, the experts of a few tokens, and the experts of many.
 //
-//   route_topk     : z = x Wr^T + b in float (x may be bf16; Wr and b are float); the `top` largest logits are chosen
-//                    (of equal logits the lower index first) and weighted by the softmax over the chosen logits only:
+//   route_topk     : z = x Wr^T + b in float (x may be bf16; Wr and b are float); top-k by z
+//                    (of equal z the lower index first), weights exp(z_e) / sum over the k winners of exp(z_c):
 //                    ids[t, k], weights[t, k], k in order of falling logit.  One warp per token.
 //   An expert is  Wd_e ( T(act(Wg_e x) * (Wu_e x)) ),  act(z) = z * sigmoid(z);  the layer's output is
 //   y[t] = T( sum_k weights[t, k] * expert_{ids[t, k]}(x[t]) ).  Wgu is [E, 2 ff, D] (gate rows over up rows), Wd is

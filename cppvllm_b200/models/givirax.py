@@ -5,7 +5,7 @@ position vector; layers that are *parallel* blocks (one RMSNorm, whose output th
 the stream receives the sum of their outputs); a final RMSNorm and an untied output head.  The mixer is grouped-query
 attention without rotation and without a value projection (the keys are the values), with a scale from the
 configuration, behind a sliding window that keeps the sequence's first tokens visible.  The feed-forward is dense
-(tanh-GELU, no gate), a mixture of gated SiLU experts with a biased float32 router and a softmax over the chosen logits,
+(tanh-GELU, no gate), a mixture of gated SiLU experts behind a biased float32 router (top-k, weights renormalised over the k winners),
 or absent.  Layers ``loop.start .. loop.stop-1`` run ``loop.times`` times in a row with the same weights and a cache of
 their own per pass; each pass begins with a learned vector added to the stream, and every pass after the first also
 with the embedding output added again.  Tensor names: ``embed``, ``pos``, ``loop.step``, ``l<i>.norm1``,

@@ -2,7 +2,7 @@
 
 * ``act_mlp``: y = Wdown act(Wup x), no gate, no biases; act = "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).
 * ``routed_glu``: a mixture of experts.  Router logits z = Wr x + b in float32 (x as the norm rounded it); each token uses
-  the ``top`` experts with the largest logits, weighted by the softmax over the chosen logits only; an expert is
+  its ``top`` best-scoring experts C, with weights w_e = exp(z_e) / sum_{c in C} exp(z_c); an expert is
   Wdown (silu(Wgate x) * (Wup x)) without biases; the output is the weighted sum of the chosen experts' outputs.  Expert e's
   tensors are ``<prefix>e<e>.gate|up|down``; they are stacked at load time into [E, 2 ff, D] (gate rows over up rows) and
   [E, D, ff], so that a kernel reaches every expert from one base address.  One or two tokens read only their chosen

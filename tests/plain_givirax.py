@@ -7,7 +7,7 @@ safetensors reading and its own arithmetic, written from the design's equations:
     mix      : q = Wq n, k = Wk n, v = k;  head h reads kv head floor(h / (H / G));  a_ij = c * q_i . k_j over the j with
                j <= i and (i - j < window or j < keep_first);  softmax over those;  y = Wo concat_h(sum_j a_ij k_j)
     ff dense : Wd gelu_tanh(Wu n)
-    ff routed: z = Wr n + b;  the `top` largest z are chosen;  weights = softmax over the chosen z only;
+    ff routed: z = Wr n + b;  C = top-k of z;  w_e = exp(z_e) / sum_{c in C} exp(z_c);
                y = sum_k weight_k * Wd_e (silu(Wg_e n) * (Wu_e n))
     passes   : layers start..stop-1 run `times` times; before pass t: x <- x + x_0 (t > 0), then x <- x + step[t]
     logits   = H (x / sqrt(mean(x^2) + eps) * w_final)

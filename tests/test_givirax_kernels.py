@@ -91,7 +91,7 @@ def test_gelu_tanh_and_key_rows_into_pages(ops, dt):
 
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("E,top,D", [(8, 2, 48), (3, 1, 50), (4, 4, 64), (40, 33, 96)])
-def test_router_chooses_the_largest_logits_and_weights_them_by_their_own_softmax(ops, dt, E, top, D):
+def test_router_top_k_and_renormalised_weights(ops, dt, E, top, D):
     g = torch.Generator().manual_seed(2)
     T = 19
     x = torch.randn(T, D, generator=g).to(dt)
