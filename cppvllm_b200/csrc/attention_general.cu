@@ -7,7 +7,9 @@
 // passed them: the token then reads 0..min(f, lo)-1 and lo..p (two runs of tiles).  The keys of the step's own tokens
 // are already in the pages (the projection kernel writes before this kernel reads).  `planes` = 2: a page is
 // [K | V][kv head][slot][hd]; `planes` = 1: a page is [kv head][slot][hd] and a key is also its value.  Queries are
-// read from rows of `q_stride` elements (the packed output of a projection, or [T, H, hd] itself).
+// read from rows of `q_stride` elements (the packed output of a projection, or [T, H, hd] itself).  With `planes` = 1 the
+// value may be narrower than the key: `vd` <= hd says how many leading elements of a key are its value (a cache of latent
+// vectors with a positional part behind them); the output rows are [T, H, vd].
 //
 // Formulas (reference kernels/paged_attention.cu:89-359 and model/model_architecture.cpp:134,147):
 //   query head h uses kv head h / (H / KV);  s_j = scale * q . k_j  for lo <= j <= p, others excluded;
@@ -26,7 +28,7 @@ __global__ void __launch_bounds__(kAttnThreads)
 paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ cache,
                                const int* __restrict__ block_tables, int table_width,
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
-                               int H, int KV, int hd, int page_size, int window, int keep_first, int planes, int q_stride,
+                               int H, int KV, int hd, int vd, int page_size, int window, int keep_first, int planes, int q_stride,
                                float scale, int num_pages, int* __restrict__ err) {
     pdl_trigger();
     pdl_wait();
@@ -86,7 +88,7 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
 #pragma unroll
         for (int i = 0; i < kMaxDimsPerThread; ++i) {
             const int d = tid + i * kAttnThreads;
-            if (d < hd) {
+            if (d < vd) {
                 float a = acc[i] * corr;
                 for (int jj = 0; jj < n; ++jj) {
                     const int64_t vo = v_off[jj];
@@ -103,7 +105,7 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
 #pragma unroll
     for (int i = 0; i < kMaxDimsPerThread; ++i) {
         const int d = tid + i * kAttnThreads;
-        if (d < hd) out[(t * H + h) * hd + d] = from_float<T>(acc[i] * inv_l);
+        if (d < vd) out[(t * H + h) * vd + d] = from_float<T>(acc[i] * inv_l);
     }
 }
 
@@ -113,7 +115,7 @@ using namespace cvb;
 
 extern "C" int cvb_paged_attention_general(void* out, const void* q, const void* cache, const int* block_tables,
                                            int table_width, const int* seq_of_token, const int* positions, int T,
-                                           int H, int KV, int hd, int page_size, int window, int keep_first, int planes,
+                                           int H, int KV, int hd, int vd, int page_size, int window, int keep_first, int planes,
                                            int q_stride, float scale, int num_pages, int dtype, int* err_flag,
                                            cudaStream_t stream) {
     if (T == 0) return CVB_OK;
@@ -121,13 +123,14 @@ extern "C" int cvb_paged_attention_general(void* out, const void* q, const void*
         return CVB_E_SIZE;
     if (hd > kAttnThreads * kMaxDimsPerThread) return CVB_E_SIZE;
     if (H % KV || (planes != 1 && planes != 2) || keep_first < 0 || q_stride < H * hd) return CVB_E_SHAPE;
+    if (vd <= 0 || vd > hd || (planes == 2 && vd != hd)) return CVB_E_SHAPE;
     if (H > 65535) return CVB_E_SIZE;
     dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>(H));
     const size_t smem = kAttnThreads * sizeof(int64_t) + (static_cast<size_t>(hd) + kAttnThreads + 32) * sizeof(float);
 #define CALL(TY)                                                                                         \
     launch_kernel(paged_attention_general_kernel<TY>, dim3(grid), dim3(kAttnThreads), smem, stream,                             \
         (TY*)out, (const TY*)q, (const TY*)cache, block_tables, table_width, seq_of_token, positions, H, \
-        KV, hd, page_size, window, keep_first, planes, q_stride, scale, num_pages, err_flag)
+        KV, hd, vd, page_size, window, keep_first, planes, q_stride, scale, num_pages, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

@@ -40,6 +40,8 @@ LIBRARIES: Dict[str, List[str]] = {
     "resid32": ["residual_f32.cu"],
     "attn_keys": ["attention_keys.cu"],
     "moe": ["moe.cu"],
+    "latent": ["latent.cu"],
+    "recurrent": ["recurrent.cu"],
     # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
 }

@@ -216,7 +216,8 @@ def _resid32_lib():
     global _resid32
     if _resid32 is None:
         lib = load_library("resid32")
-        for name in ("cvb_embed_positions", "cvb_resid_update", "cvb_gelu_tanh", "cvb_write_rows"):
+        for name in ("cvb_embed_positions", "cvb_resid_update", "cvb_gelu_tanh", "cvb_write_rows", "cvb_norm_add", "cvb_bias_act",
+                     "cvb_gated_norm"):
             getattr(lib, name).restype = c_int
         _resid32 = lib
     return _resid32
@@ -289,6 +290,206 @@ def write_rows(pages: torch.Tensor, src: torch.Tensor, slots: torch.Tensor, col0
                                          c_int(heads), c_int(width), c_int(page_size), c_int64(pages.numel()),
                                          c_int(dtype_code(src.dtype)), _ptr(error_flag(src.device)), _stream()), "write_rows")
     return pages
+
+
+def norm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, bias: Optional[torch.Tensor] = None,
+             accumulate: bool = True, copy: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """h (float32 [T, D]) <- [h +] RMSNorm(y + bias) * weight: the norm behind a sublayer, whose result alone joins the stream
+    (`accumulate=False`: h is set, not added to).  `copy` (the activations' type, shaped like h) receives the new stream
+    rounded once."""
+    _cuda(h, y, weight, bias, copy); _contig(h, y, weight, bias, copy)
+    T, D = h.shape
+    if (h.dtype != torch.float32 or y.shape != h.shape or weight.dtype != torch.float32 or weight.numel() != D
+            or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != D))
+            or (copy is not None and (copy.shape != h.shape or copy.dtype != y.dtype))):
+        raise KernelError("norm_add: h float32 [T, D]; y [T, D]; weight and bias float32 [D]; copy like y")
+    _check(_resid32_lib().cvb_norm_add(_ptr(h), _ptr(y), _ptr(bias), _ptr(weight), _ptr(copy), c_int(T), c_int(D), c_float(eps),
+                                       c_int(1 if accumulate else 0), c_int(dtype_code(y.dtype)), _stream()), "norm_add")
+    return h
+
+
+ACTIVATIONS = {"none": 0, "relu2": 1, "gelu_tanh": 2}
+
+
+def bias_act(out: torch.Tensor, x: torch.Tensor, bias: Optional[torch.Tensor], activation: str) -> torch.Tensor:
+    """out = act(x + bias) over rows of bias.numel() elements; act = none | relu2 (the square of relu) | gelu_tanh."""
+    _cuda(out, x, bias); _contig(out, x, bias)
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"bias_act: activation '{activation}' is not built; built: {sorted(ACTIVATIONS)}")
+    D = x.shape[-1]
+    if out.shape != x.shape or out.dtype != x.dtype or (bias is not None and (bias.dtype != torch.float32 or bias.numel() != D)):
+        raise KernelError("bias_act: out like x; bias float32 [D]")
+    _check(_resid32_lib().cvb_bias_act(_ptr(out), _ptr(x), _ptr(bias), c_int64(x.numel()), c_int(D), c_int(ACTIVATIONS[activation]),
+                                       c_int(dtype_code(x.dtype)), _stream()), "bias_act")
+    return out
+
+
+def gated_norm(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, groups: int, eps: float) -> torch.Tensor:
+    """out[t, g, :] = RMSNorm(o[t, g, :]) * weight * sigmoid(gate[t, g, :]) over `groups` groups of weight.numel() elements;
+    o float32 [T, groups * G]; gate a view of [T, groups * G] columns inside rows of gate.stride(0) elements."""
+    _cuda(out, o, gate, weight); _contig(out, o, weight)
+    T = o.shape[0]
+    G = weight.numel()
+    if (o.dtype != torch.float32 or o.shape[1] != groups * G or out.shape != o.shape or gate.dtype != out.dtype or gate.dim() != 2
+            or gate.shape != o.shape or gate.stride(1) != 1 or weight.dtype != torch.float32):
+        raise KernelError("gated_norm: o float32 [T, groups * G]; out and gate [T, groups * G] of the activations' type; weight float32 [G]")
+    _check(_resid32_lib().cvb_gated_norm(_ptr(out), _ptr(o), _ptr(gate), c_int(gate.stride(0)), _ptr(weight), c_int(T), c_int(groups),
+                                         c_int(G), c_float(eps), c_int(dtype_code(out.dtype)), _stream()), "gated_norm")
+    return out
+
+
+# ---- attention over a cache of latent vectors: what stands around the attention kernel ------------------------------
+
+_latent = None
+
+
+def _latent_lib():
+    global _latent
+    if _latent is None:
+        lib = load_library("latent")
+        for name in ("cvb_latent_prep", "cvb_latent_q_assemble", "cvb_head_gate"):
+            getattr(lib, name).restype = c_int
+        _latent = lib
+    return _latent
+
+
+def latent_prep(packed: torch.Tensor, cq_out: Optional[torch.Tensor], q_off: int, q_rank: int, q_weight: Optional[torch.Tensor],
+                pages: Optional[torch.Tensor], kv_off: int, rank: int, rot_width: int, rot: int, kv_weight: Optional[torch.Tensor],
+                cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], positions: torch.Tensor, slots: Optional[torch.Tensor],
+                eps: float) -> None:
+    """Per row of `packed`: cq_out = RMSNorm(packed[q_off : q_off + q_rank]) * q_weight, and into the row's cache slot
+    [RMSNorm(packed[kv_off : kv_off + rank]) * kv_weight | rotation of the rot_width elements behind them] (their first `rot`
+    elements turn in pairs (2i, 2i+1) by cos/sin[position]).  `cq_out` or `pages` may be None."""
+    _cuda(packed, cq_out, q_weight, pages, kv_weight, cos, sin, positions, slots)
+    _contig(packed, cq_out, q_weight, pages, kv_weight, cos, sin, positions, slots)
+    T = packed.shape[0]
+    for t in (cq_out, pages):
+        if t is not None and t.dtype != packed.dtype:
+            raise KernelError("latent_prep: outputs share the packed rows' element type")
+    for t in (q_weight, kv_weight, cos, sin):
+        if t is not None and t.dtype != torch.float32:
+            raise KernelError("latent_prep: norm weights and angle tables are float32")
+    if positions.dtype != torch.int32 or (slots is not None and slots.dtype != torch.int32):
+        raise KernelError("latent_prep: positions and slots are int32")
+    if pages is not None and (slots is None or (rot > 0 and (cos is None or cos.shape[1] != rot // 2))):
+        raise KernelError("latent_prep: a cache write needs slots and angle tables [positions, rot / 2]")
+    total_slots = pages.numel() // (rank + rot_width) if pages is not None else 0
+    _check(_latent_lib().cvb_latent_prep(
+        _ptr(cq_out), _ptr(pages), _ptr(packed), c_int(T), c_int(packed.shape[1]), c_int(q_off), c_int(q_rank), _ptr(q_weight),
+        c_int(kv_off), c_int(rank), c_int(rot_width), c_int(rot), _ptr(kv_weight), _ptr(cos), _ptr(sin),
+        c_int(cos.shape[0] if cos is not None else 1), _ptr(positions), _ptr(slots), c_int64(total_slots), c_float(eps),
+        c_int(dtype_code(packed.dtype)), _ptr(error_flag(packed.device)), _stream()), "latent_prep")
+
+
+def latent_q_assemble(q_out: torch.Tensor, q_abs: torch.Tensor, q: torch.Tensor, num_heads: int, nope: int, rank: int, rot_width: int,
+                      rot: int, cos: torch.Tensor, sin: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    """q_out[t, h] = [q_abs[h, t, :rank] | rotation of q[t, h, nope : nope + rot_width]]."""
+    _cuda(q_out, q_abs, q, cos, sin, positions); _contig(q_out, q_abs, q, cos, sin, positions)
+    T = q.shape[0]
+    if (q_out.dtype != q.dtype or q_abs.dtype != q.dtype or cos.dtype != torch.float32 or sin.dtype != torch.float32
+            or positions.dtype != torch.int32 or q_out.numel() != T * num_heads * (rank + rot_width)
+            or q_abs.numel() != T * num_heads * rank or (rot > 0 and cos.shape[1] != rot // 2)):
+        raise KernelError("latent_q_assemble: q [T, H * (nope + rot_width)], q_abs [H, T, rank], q_out [T, H, rank + rot_width]")
+    _check(_latent_lib().cvb_latent_q_assemble(
+        _ptr(q_out), _ptr(q_abs), _ptr(q), c_int(T), c_int(q.shape[1]), c_int(num_heads), c_int(nope), c_int(rank), c_int(rot_width),
+        c_int(rot), _ptr(cos), _ptr(sin), c_int(cos.shape[0]), _ptr(positions), c_int(dtype_code(q.dtype)),
+        _ptr(error_flag(q.device)), _stream()), "latent_q_assemble")
+    return q_out
+
+
+def head_gate(out: torch.Tensor, o: torch.Tensor, gate: torch.Tensor, num_heads: int, vdim: int) -> torch.Tensor:
+    """out[t, h * vdim + j] = o[h, t, j] * sigmoid(gate[t, h]); gate is a view of H columns inside rows of gate.stride(0)."""
+    _cuda(out, o, gate); _contig(out, o)
+    T = out.shape[0]
+    if (out.dtype != o.dtype or gate.dtype != o.dtype or out.shape[1] != num_heads * vdim or o.numel() != T * num_heads * vdim
+            or gate.shape != (T, num_heads) or gate.stride(1) != 1):
+        raise KernelError("head_gate: o [H, T, vdim], out [T, H * vdim], gate [T, H] of one element type")
+    _check(_latent_lib().cvb_head_gate(_ptr(out), _ptr(o), _ptr(gate), c_int(T), c_int(gate.stride(0)), c_int(num_heads), c_int(vdim),
+                                       c_int(dtype_code(o.dtype)), _stream()), "head_gate")
+    return out
+
+
+# ---- mixers with a matrix of fixed size per request and head -------------------------------------------------------------
+
+_recurrent = None
+
+
+def _recurrent_lib():
+    global _recurrent
+    if _recurrent is None:
+        lib = load_library("recurrent")
+        for name in ("cvb_lightning_scan", "cvb_delta_prep", "cvb_conv_history", "cvb_delta_scan"):
+            getattr(lib, name).restype = c_int
+        _recurrent = lib
+    return _recurrent
+
+
+def _state_args(state: torch.Tensor):
+    if state.dtype != torch.float32 or not state.is_contiguous() or state.dim() != 2:
+        raise KernelError("a recurrent state is float32 [slots, floats]")
+    return _ptr(state), c_int64(state.shape[1]), state.shape[0]
+
+
+def lightning_scan(out: torch.Tensor, packed: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, decay: torch.Tensor,
+                   cu_seqlens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, num_heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Per request and head, over the request's tokens of this step: S <- decay_h S + k v^T, out = S^T q with q, k, v = silu of
+    the packed projection's columns; S [dim, vdim] float32 at the front of the request's state row.  out float32 [T, H * vdim]."""
+    _cuda(out, packed, state, decay, cu_seqlens, state_slots); _contig(out, packed, decay, cu_seqlens, state_slots)
+    sp, sf, n_slots = _state_args(state)
+    if (out.dtype != torch.float32 or out.shape != (packed.shape[0], num_heads * vdim) or decay.dtype != torch.float32
+            or decay.numel() != num_heads or cu_seqlens.dtype != torch.int32 or state_slots.dtype != torch.int32):
+        raise KernelError("lightning_scan: out float32 [T, H * vdim]; decay float32 [H]; cu_seqlens, state_slots int32")
+    _check(_recurrent_lib().cvb_lightning_scan(
+        _ptr(out), _ptr(packed), c_int(packed.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off), sp, sf, _ptr(decay), _ptr(cu_seqlens),
+        _ptr(state_slots), c_int(n_slots), c_int(num_seqs), c_int(num_heads), c_int(dim), c_int(vdim), c_int(dtype_code(packed.dtype)),
+        _ptr(error_flag(out.device)), _stream()), "lightning_scan")
+    return out
+
+
+def delta_prep(qn, kn, vv, gg, bb, packed: torch.Tensor, qkv_off: int, conv_w: torch.Tensor, a: torch.Tensor, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, b: torch.Tensor, state: torch.Tensor, conv_off: int, seq_of_token, cu_seqlens, state_slots,
+               num_heads: int, num_kv_heads: int, dim: int, vdim: int) -> None:
+    """Per token: convolutions with silu, unit q and k, sigmoid(b), the decay; all outputs float32 (see csrc/recurrent.cu)."""
+    _cuda(qn, kn, vv, gg, bb, packed, conv_w, a, dt_bias, a_log, b, state, seq_of_token, cu_seqlens, state_slots)
+    _contig(qn, kn, vv, gg, bb, packed, conv_w, a, dt_bias, a_log, b, seq_of_token, cu_seqlens, state_slots)
+    sp, sf, n_slots = _state_args(state)
+    T = packed.shape[0]
+    H, G = num_heads, num_kv_heads
+    C = 2 * G * dim + H * vdim
+    for t_, n_ in ((qn, T * G * dim), (kn, T * G * dim), (vv, T * H * vdim), (gg, T * H * dim), (bb, T * H), (a, T * H * dim), (b, T * H),
+                   (dt_bias, H * dim), (a_log, H)):
+        if t_.dtype != torch.float32 or t_.numel() != n_:
+            raise KernelError("delta_prep: float32 buffers of the sizes the head counts give")
+    if conv_w.dtype != torch.float32 or conv_w.dim() != 2 or conv_w.shape[0] != C:
+        raise KernelError("delta_prep: conv_w float32 [channels, taps]")
+    _check(_recurrent_lib().cvb_delta_prep(
+        _ptr(qn), _ptr(kn), _ptr(vv), _ptr(gg), _ptr(bb), _ptr(packed), c_int(T), c_int(packed.shape[1]), c_int(qkv_off), _ptr(conv_w),
+        c_int(conv_w.shape[1]), _ptr(a), _ptr(dt_bias), _ptr(a_log), _ptr(b), sp, sf, c_int64(conv_off), _ptr(seq_of_token),
+        _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots), c_int(H), c_int(G), c_int(dim), c_int(vdim), c_int(dtype_code(packed.dtype)),
+        _ptr(error_flag(packed.device)), _stream()), "delta_prep")
+
+
+def conv_history(state: torch.Tensor, conv_off: int, packed: torch.Tensor, qkv_off: int, channels: int, taps: int, cu_seqlens,
+                 state_slots, num_seqs: int) -> None:
+    """The last taps - 1 raw inputs of every request's portion (older ones from the old history) become its history."""
+    _cuda(state, packed, cu_seqlens, state_slots); _contig(packed, cu_seqlens, state_slots)
+    sp, sf, n_slots = _state_args(state)
+    _check(_recurrent_lib().cvb_conv_history(sp, sf, c_int64(conv_off), _ptr(packed), c_int(packed.shape[1]), c_int(qkv_off), c_int(channels),
+                                             c_int(taps), _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots), c_int(num_seqs),
+                                             c_int(dtype_code(packed.dtype)), _stream()), "conv_history", kernels=1 if taps > 1 else 0)
+
+
+def delta_scan(out, qn, kn, vv, gg, bb, state: torch.Tensor, cu_seqlens, state_slots, num_seqs: int, num_heads: int, num_kv_heads: int,
+               dim: int, vdim: int) -> torch.Tensor:
+    """Per request and head: S <- diag(g) S; u = b (v - S^T k); S <- S + k u^T; out = S^T q.  out float32 [T, H * vdim]."""
+    _cuda(out, qn, kn, vv, gg, bb, state, cu_seqlens, state_slots); _contig(out, qn, kn, vv, gg, bb, cu_seqlens, state_slots)
+    sp, sf, n_slots = _state_args(state)
+    if out.dtype != torch.float32:
+        raise KernelError("delta_scan: out is float32")
+    _check(_recurrent_lib().cvb_delta_scan(_ptr(out), _ptr(qn), _ptr(kn), _ptr(vv), _ptr(gg), _ptr(bb), sp, sf, _ptr(cu_seqlens),
+                                           _ptr(state_slots), c_int(n_slots), c_int(num_seqs), c_int(num_heads), c_int(num_kv_heads),
+                                           c_int(dim), c_int(vdim), _ptr(error_flag(out.device)), _stream()), "delta_scan")
+    return out
 
 
 # ---- attention over keys that are also the values ------------------------------------------------------------------
@@ -544,11 +745,13 @@ def qk_norm_rope_kv(q_out: torch.Tensor, qkv: torch.Tensor, q_weight: Optional[t
 def paged_attention_general(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
                             seq_of_token: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
                             head_dim: int, page_size: int, scale: float, window: int = 0,
-                            num_tokens: Optional[int] = None, keep_first: int = 0, keys_are_values: bool = False) -> torch.Tensor:
+                            num_tokens: Optional[int] = None, keep_first: int = 0, keys_are_values: bool = False,
+                            value_dim: Optional[int] = None) -> torch.Tensor:
     """One block per (token, query head); any head size.  `keep_first`: positions 0..keep_first-1 stay visible behind the
     window.  `keys_are_values`: pages are [kv head, slot, head_dim] and a key is also its value (else [K|V, kv head, slot,
     head_dim]).  `q` may be the packed output of a projection: rows of q.shape[1] elements whose first H * head_dim are
-    the queries."""
+    the queries.  `value_dim` (with keys_are_values): only the first value_dim elements of a key are its value; out is
+    [T, H, value_dim]."""
     _cuda(out, q, cache, block_tables, seq_of_token, positions)
     _contig(out, q, cache, block_tables, seq_of_token, positions)
     T = q.shape[0] if num_tokens is None else num_tokens
@@ -561,12 +764,17 @@ def paged_attention_general(out: torch.Tensor, q: torch.Tensor, cache: torch.Ten
     if num_heads % num_kv_heads:
         raise KernelError(f"paged_attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
     planes = 1 if keys_are_values else 2
+    vd = head_dim if value_dim is None else int(value_dim)
+    if vd != head_dim and not keys_are_values:
+        raise KernelError("paged_attention: a value narrower than the key needs keys that are the values")
+    if out.numel() < T * num_heads * vd:
+        raise KernelError("paged_attention: out is too small")
     page_elems = planes * num_kv_heads * page_size * head_dim
     num_pages = cache.numel() // page_elems
     q_stride = q.shape[1] if q.dim() == 2 else num_heads * head_dim
     _check(core().cvb_paged_attention_general(
         _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_of_token),
-        _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+        _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(vd), c_int(page_size),
         c_int(window), c_int(keep_first), c_int(planes), c_int(q_stride), c_float(scale), c_int(num_pages),
         c_int(dtype_code(q.dtype)),
         _ptr(error_flag(q.device)), _stream()), "paged_attention_general")

@@ -9,6 +9,13 @@
 //   gelu_tanh       : out = T( 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))) ), z = float(x)
 //   write_rows      : rows of a packed projection into cache pages [page, heads, slot in page, width] (a cache that
 //                     holds one vector per token and head: keys that also serve as values)
+//   norm_add        : h[t, :] <- [h[t, :] +] (y + b) / sqrt(mean((y + b)^2) + eps) * w, with y a sublayer's output and b an
+//                     optional bias: the norm sits behind the sublayer and only its result joins the stream.  A copy of the
+//                     new stream in the activations' type is written beside it (what the next sublayer's products read).
+//   bias_act        : out = T( act(x + b) ), act = identity | relu(z)^2 | tanh-GELU
+//   gated_norm      : out[t, g, j] = T( o / sqrt(mean_j(o[t, g, :]^2) + eps) * w[j] * sigmoid(gate[t, g, j]) ) over groups of
+//                     equal size (one group: a norm over the whole row; one group per head: a norm per head with a weight
+//                     that the heads share); o is float, the gate a column range of a packed projection
 //
 // T is the activations' element type (float or bf16); deltas d1, d2 and the norm's output have it.
 #include "common.cuh"
@@ -166,6 +173,67 @@ __global__ void gelu_tanh_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const _
     }
 }
 
+// The norm behind a sublayer: only the normed output joins the stream.
+template <typename T>
+__global__ void __launch_bounds__(kUpdateThreads)
+norm_add_kernel(float* __restrict__ h, const T* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ w,
+                T* __restrict__ copy, int D, float eps, int accumulate) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const T* yr = y + row * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += kUpdateThreads) {
+        const float v = to_float(yr[i]) + (bias ? bias[i] : 0.f);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / static_cast<float>(D) + eps);
+    for (int i = threadIdx.x; i < D; i += kUpdateThreads) {
+        const float v = to_float(yr[i]) + (bias ? bias[i] : 0.f);
+        const float r = (accumulate ? h[row * D + i] : 0.f) + v * inv * w[i];
+        h[row * D + i] = r;
+        if (copy) copy[row * D + i] = from_float<T>(r);
+    }
+}
+
+template <typename T>
+__global__ void bias_act_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ bias, int64_t n, int D,
+                                int act) {
+    pdl_trigger();
+    pdl_wait();
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        float z = to_float(x[i]) + (bias ? bias[i % D] : 0.f);
+        if (act == 1) { z = fmaxf(z, 0.f); z = z * z; }
+        else if (act == 2) z = gelu_tanh_of(z);
+        out[i] = from_float<T>(z);
+    }
+}
+
+// One block per token; a warp takes a group at a time.
+template <typename T>
+__global__ void __launch_bounds__(kUpdateThreads)
+gated_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
+                  const float* __restrict__ w, int groups, int G, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    const int64_t row = blockIdx.x;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = kUpdateThreads >> 5;
+    for (int g = warp; g < groups; g += n_warps) {
+        const float* og = o + (row * groups + g) * G;
+        float ss = 0.f;
+        for (int j = lane; j < G; j += 32) ss = fmaf(og[j], og[j], ss);
+        ss = warp_sum(ss);
+        const float inv = 1.f / sqrtf(ss / static_cast<float>(G) + eps);
+        for (int j = lane; j < G; j += 32) {
+            const float z = to_float(gate[row * gate_stride + g * G + j]);
+            out[(row * groups + g) * G + j] = from_float<T>(og[j] * inv * w[j] * (1.f / (1.f + expf(-z))));
+        }
+    }
+}
+
 // src row t holds, from column col0 on, `heads` vectors of `width` elements; they land at
 // pages[slot / page_size, head, slot % page_size, :].
 template <typename T>
@@ -245,6 +313,41 @@ extern "C" int cvb_write_rows(void* pages, const void* src, const int* slots, in
     if (T < 0 || heads <= 0 || width <= 0 || page_size <= 0 || row_stride < col0 + heads * width || col0 < 0) return CVB_E_SIZE;
 #define CALL(TY) launch_kernel(write_rows_kernel<TY>, dim3(T), dim3(128), 0, stream, (TY*)pages, (const TY*)src, slots, \
                                row_stride, col0, heads, width, page_size, page_elems_total, err_flag)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_norm_add(float* h, const void* y, const float* bias, const float* w, void* copy, int T, int D, float eps,
+                            int accumulate, int dtype, cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || D <= 0) return CVB_E_SIZE;
+    if (h == nullptr || y == nullptr || w == nullptr) return CVB_E_SHAPE;
+#define CALL(TY) launch_kernel(norm_add_kernel<TY>, dim3(T), dim3(kUpdateThreads), 0, stream, h, (const TY*)y, bias, w, (TY*)copy, \
+                               D, eps, accumulate)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_bias_act(void* out, const void* x, const float* bias, int64_t n, int D, int act, int dtype, cudaStream_t stream) {
+    if (n == 0) return CVB_OK;
+    if (n < 0 || D <= 0 || act < 0 || act > 2) return CVB_E_SIZE;
+    const int64_t want = (n + 255) / 256;
+    const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
+#define CALL(TY) launch_kernel(bias_act_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)x, bias, n, D, act)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_gated_norm(void* out, const float* o, const void* gate, int gate_stride, const float* w, int T, int groups, int G,
+                              float eps, int dtype, cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || groups <= 0 || G <= 0) return CVB_E_SIZE;
+    if (gate_stride < groups * G) return CVB_E_SHAPE;
+#define CALL(TY) launch_kernel(gated_norm_kernel<TY>, dim3(T), dim3(kUpdateThreads), 0, stream, (TY*)out, o, (const TY*)gate, \
+                               gate_stride, w, groups, G, eps)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

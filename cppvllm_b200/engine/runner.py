@@ -84,7 +84,8 @@ class ModelRunner:
         self.max_model_len = int(min(max_model_len, spec.max_positions) if spec.max_positions else max_model_len)
         self.workspace = Workspace(self.device, self.max_step_tokens, self.max_seqs)
         stream_dtype = {None: None, "float32": torch.float32}[spec.residual_dtype]
-        self.rt = Runtime(self.device, dtype, self.workspace, plain_kernels=bool(use_ref_kernels), residual_dtype=stream_dtype)
+        self.rt = Runtime(self.device, dtype, self.workspace, plain_kernels=bool(use_ref_kernels), residual_dtype=stream_dtype,
+                          max_positions=self.max_model_len)
         self.model = CausalLM(spec, self.rt)
         self.model.bind(load_weights(self.model, model_dir, self.device, dtype))
         self.vocab_size = self.model.vocab_size

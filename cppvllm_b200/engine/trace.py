@@ -13,7 +13,8 @@ of a step run as one batch.  A request is admitted at its first appearance, may 
 what it holds when it is named in ``end``.  For a step in which something is wanted, ``<out>/<step>.f32``
 receives the logits as little-endian float32 [wanted, vocab], in the order of the entries and of ``want``.
 After every step the line ``done <step>`` is printed and flushed.  The cache pool holds ``--max-tokens`` tokens
-(a multiple of the page size), so pages are used again as requests end.
+(a multiple of the page size) and there are ``--state-slots`` slots of per-request state, so pages and slots are used again
+as requests end.
 """
 from __future__ import annotations
 
@@ -35,6 +36,8 @@ def build_parser() -> argparse.ArgumentParser:
                    help="tokens the cache pool holds (each live request's count rounded up to a multiple of 64)")
     p.add_argument("--block-size", type=int, default=32, help="tokens per cache page (must divide 64)")
     p.add_argument("--max-num-seqs", type=int, default=16, help="most requests in one step")
+    p.add_argument("--state-slots", type=int, default=4,
+                   help="requests that can be live at once: slots of per-request state, used again as requests end")
     p.add_argument("--enforce-eager", action="store_true", help="never replay CUDA graphs for decode-only steps")
     p.add_argument("--use-ref-kernels", action="store_true", help="plain twin kernels only (general attention, library products)")
     return p
@@ -58,6 +61,7 @@ def main(argv=None) -> int:
     runner = ModelRunner(args.model, dtype=parse_dtype(args.dtype), device="cuda:0", page_size=ps,
                          num_pages=num_pages, max_step_tokens=max(64, min(args.max_tokens, 32768)),
                          max_seqs=args.max_num_seqs, max_model_len=max(64, args.max_tokens),
+                         num_state_slots=max(1, args.state_slots),
                          enforce_eager=args.enforce_eager, use_ref_kernels=args.use_ref_kernels)
     for line in sys.stdin:
         line = line.strip()

@@ -1,2 +1,2 @@
 """Architectures.  Importing this package registers them."""
-from . import givirax, qwen3  # noqa: F401
+from . import dugulorn, givirax, qwen3  # noqa: F401

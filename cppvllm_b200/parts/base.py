@@ -62,7 +62,7 @@ def build_part(category: str, spec, runtime, **extra):
 
 @dataclass(frozen=True)
 class WeightSpec:
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]    # a size of -1 is taken from the checkpoint (an inner rank that no configuration key names)
     role: str = "matrix"      # "matrix": operand of a matrix product / embedding table (engine dtype, or float32
                               #           if stored so); "vector": norm weights and the like (always float32);
                               # "int_table": integer look-up table (int32)
@@ -168,6 +168,7 @@ class Runtime:
     workspace: Workspace
     plain_kernels: bool = False
     residual_dtype: Optional[torch.dtype] = None      # element type of the residual stream; None = the activations' type
+    max_positions: int = 0                            # positions the engine will ever feed (tables of a model that names no limit)
 
     @property
     def stream_dtype(self) -> torch.dtype:

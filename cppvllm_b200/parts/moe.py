@@ -1,6 +1,7 @@
 """Feed-forward parts beside the gated dense one (parts/mlp.py):
 
-* ``act_mlp``: y = Wdown act(Wup x), no gate, no biases; act = "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))).
+* ``act_mlp``: y = Wdown act(Wup x [+ b_up]) [+ b_down], no gate; act = "gelu_tanh" (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))))
+  or "relu2" (relu(z)^2); ``bias=True`` adds the two bias vectors ``<up>.b`` and ``<down>.b``.
 * ``routed_glu``: a mixture of experts.  Router logits z = Wr x + b in float32 (x as the norm rounded it); each token uses
   its ``top`` best-scoring experts C, with weights w_e = exp(z_e) / sum_{c in C} exp(z_c); an expert is
   Wdown (silu(Wgate x) * (Wup x)) without biases; the output is the weighted sum of the chosen experts' outputs.  Expert e's
@@ -23,20 +24,27 @@ from .base import FeedForward, WeightSpec, register_part
 @register_part("ffn", "act_mlp")
 class ActMLP(FeedForward):
     def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int, activation: str = "gelu_tanh",
-                 up_name: str = "up", down_name: str = "down"):
+                 up_name: str = "up", down_name: str = "down", bias: bool = False):
         super().__init__(runtime, prefix, names)
-        if activation != "gelu_tanh":
-            raise ValueError(f"activation '{activation}' is not built; built: gelu_tanh")
+        if activation not in ("gelu_tanh", "relu2"):
+            raise ValueError(f"activation '{activation}' is not built; built: gelu_tanh, relu2")
         self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.activation, self.bias = activation, bool(bias)
         self.up_name, self.down_name = up_name, down_name
-        self.w_up = self.w_down = None
+        self.w_up = self.w_down = self.b_up = self.b_down = None
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, I = self.hidden_size, self.intermediate_size
-        return {self.full_name(self.up_name): WeightSpec((I, D)), self.full_name(self.down_name): WeightSpec((D, I))}
+        specs = {self.full_name(self.up_name): WeightSpec((I, D)), self.full_name(self.down_name): WeightSpec((D, I))}
+        if self.bias:
+            specs[self.full_name(self.up_name + ".b")] = WeightSpec((I,), role="vector")
+            specs[self.full_name(self.down_name + ".b")] = WeightSpec((D,), role="vector")
+        return specs
 
     def bind(self, tensors) -> None:
         self.w_up, self.w_down = tensors[self.full_name(self.up_name)], tensors[self.full_name(self.down_name)]
+        if self.bias:
+            self.b_up, self.b_down = tensors[self.full_name(self.up_name + ".b")], tensors[self.full_name(self.down_name + ".b")]
 
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_up, self.w_down))
@@ -44,12 +52,20 @@ class ActMLP(FeedForward):
     def _project(self, x, w, out, rows):
         return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
 
-    def forward(self, x, ctx):
+    def forward_unbiased(self, x, ctx):
+        """(Wdown act(Wup x + b_up), b_down): for a caller whose next kernel adds the output bias itself."""
         T = x.shape[0]
         ws = self.rt.workspace
         up = self._project(x, self.w_up, ws.rows("ffn_up", T, self.intermediate_size, x.dtype), T)
-        ops.gelu_tanh(up, up)
-        return self._project(up, self.w_down, ws.rows("ffn_out", T, self.hidden_size, x.dtype), T)
+        if self.activation == "gelu_tanh" and self.b_up is None:
+            ops.gelu_tanh(up, up)
+        else:
+            ops.bias_act(up, up, self.b_up, self.activation)
+        return self._project(up, self.w_down, ws.rows("ffn_out", T, self.hidden_size, x.dtype), T), self.b_down
+
+    def forward(self, x, ctx):
+        y, bias = self.forward_unbiased(x, ctx)
+        return ops.bias_act(y, y, bias, "none") if bias is not None else y
 
 
 @register_part("ffn", "routed_glu")

@@ -37,6 +37,12 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+def _shape_fits(found, declared) -> bool:
+    """A declared size of -1 takes whatever the checkpoint holds."""
+    found, declared = tuple(found), tuple(declared)
+    return len(found) == len(declared) and all(d < 0 or d == f for f, d in zip(found, declared))
+
+
 def _convert(t: torch.Tensor, spec: WeightSpec, act_dtype: torch.dtype) -> torch.Tensor:
     if spec.role == "int_table":
         return t.to(torch.int32)
@@ -66,7 +72,7 @@ def load_weights(model, model_dir: str, device, act_dtype: torch.dtype) -> Dict[
         unexpected = sorted(n for n in where if n not in expected and n not in ignorable)
         wrong = []
         for n, spec in expected.items():
-            if n in where and tuple(where[n].shape(n)) != tuple(spec.shape):
+            if n in where and not _shape_fits(where[n].shape(n), spec.shape):
                 wrong.append(f"{n}: checkpoint {list(where[n].shape(n))}, model {list(spec.shape)}")
         for n, spec in expected.items():
             if n in where and spec.role != "int_table" and not where[n].dtype(n).is_floating_point:

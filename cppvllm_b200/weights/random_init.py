@@ -16,9 +16,12 @@ from typing import Any, Dict, Mapping
 import torch
 
 from ..config.registry import resolve_architecture
-from ..parts.base import Runtime, Workspace
+from ..parts.base import Runtime, WeightSpec, Workspace
 from ..parts.model import CausalLM
 from .safetensors_io import save_safetensors
+
+
+FREE_SIZE = 16        # what a size left to the checkpoint becomes in a random model
 
 
 def _tensor_seed(seed: int, name: str) -> int:
@@ -37,6 +40,8 @@ def random_tensors(config_dict: Mapping[str, Any], seed: int, std: float = 0.02,
     for name, ws in sorted(model.weight_specs().items()):
         g = torch.Generator(device="cpu")
         g.manual_seed(_tensor_seed(seed, name))
+        if any(d < 0 for d in ws.shape):                      # a size the checkpoint decides: the writer has to choose one
+            ws = WeightSpec(tuple(FREE_SIZE if d < 0 else d for d in ws.shape), ws.role, ws.init)
         if ws.role == "int_table":
             out[name] = torch.randint(0, 2 ** 15, ws.shape, generator=g, dtype=torch.int32)
             continue
