@@ -13,6 +13,8 @@
 // reads it transposed (ldmatrix.trans); a cache with separate values would move twice the bytes.  Four warps, each 16
 // rows: `mma.sync.m16n8k16` in bf16 with float accumulation, the softmax online in base 2.  Rows are padded by 16 bytes,
 // which makes every ldmatrix conflict-free for all head sizes that are multiples of 16.
+// The value may be narrower than the key (`vd` <= HD, a multiple of 16): only the first vd elements of a key are its value
+// (a latent vector with a positional part behind it); O += P K then stops at column vd and the output rows are [T, H, vd].
 #include "common.cuh"
 #include "sm100.cuh"
 
@@ -31,6 +33,7 @@ struct KeysAttnParams {
     const int* cu_seqlens;              // [S + 1]
     const int* positions;               // [T]
     int q_stride, table_width, S, H, KV, page_size, window, keep_first, num_pages;
+    int vd;                             // leading elements of a key that are its value (HD: all of them)
     int page_shift;                     // log2(page_size) if that is a power of two, else -1
     // decode form only: the key tiles of a (request, kv head) are shared out among `splits` blocks (gridDim.z); with more
     // than one, a block leaves its part (unnormalised rows, maxima, sums) in `parts` and a second kernel merges them
@@ -234,6 +237,7 @@ attn_keys_kernel(const KeysAttnParams p) {
                 a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
 #pragma unroll
                 for (int dp = 0; dp < HD / 16; ++dp) {
+                    if (dp * 16 >= p.vd) break;
                     uint32_t b[4];
                     ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 + ((lane >> 4) & 1) * 8);
                     mma_16816(o[dp * 2], a, b[0], b[1]);
@@ -255,10 +259,11 @@ attn_keys_kernel(const KeysAttnParams p) {
         const int tok = r / g;
         if (tok >= n_tok) continue;
         const float inv = l[half] > 0.f ? 1.f / l[half] : 0.f;
-        __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD;
+        __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * p.vd;
 #pragma unroll
         for (int dt = 0; dt < HD / 8; ++dt) {
             const int d = dt * 8 + ((lane & 3) << 1);
+            if (d >= p.vd) break;
             *reinterpret_cast<__nv_bfloat162*>(dst + d) = __floats2bfloat162_rn(o[dt][half * 2] * inv, o[dt][half * 2 + 1] * inv);
         }
     }
@@ -422,6 +427,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
             a[3] = pack2(s[kk * 2 + 1][2], s[kk * 2 + 1][3]);
 #pragma unroll
             for (int dp = 0; dp < HD / 16; ++dp) {
+                if (dp * 16 >= p.vd) break;
                 uint32_t b[4];
                 ldm_x4_trans(b, tile + (kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LD + dp * 16 + ((lane >> 4) & 1) * 8);
                 mma_16816(o[dp * 2], a, b[0], b[1]);
@@ -454,6 +460,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
     __syncthreads();
     for (int i = threadIdx.x; i < g * HD; i += kDecWarps * 32) {
         const int r = i / HD, d = i - r * HD;
+        if (d >= p.vd) continue;
         float mm = -INFINITY;
 #pragma unroll
         for (int w = 0; w < kDecWarps; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
@@ -466,7 +473,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
             acc += reinterpret_cast<const float*>(sK + w * 2 * kDecKeys * LD)[r * HD + d] * f;
         }
         if (p.splits == 1) {
-            p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+            p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * p.vd + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
         } else {
             float* dst = p.parts + ((static_cast<int64_t>(seq) * p.KV + kvh) * p.splits + blockIdx.z) * 16 * (HD + 2) + r * (HD + 2);
             dst[d] = acc;
@@ -486,6 +493,7 @@ __global__ void attn_keys_merge_kernel(const KeysAttnParams p) {
     const float* base = p.parts + (static_cast<int64_t>(seq) * p.KV + kvh) * p.splits * 16 * (HD + 2);
     for (int i = threadIdx.x; i < g * HD; i += blockDim.x) {
         const int r = i / HD, d = i - r * HD;
+        if (d >= p.vd) continue;
         float mm = -INFINITY;
         for (int z = 0; z < p.splits; ++z) mm = fmaxf(mm, base[(z * 16 + r) * (HD + 2) + HD]);
         float ll = 0.f, acc = 0.f;
@@ -495,7 +503,7 @@ __global__ void attn_keys_merge_kernel(const KeysAttnParams p) {
             ll += row[HD + 1] * f;
             acc += row[d] * f;
         }
-        p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        p.out[(static_cast<int64_t>(t) * p.H + kvh * g + r) * p.vd + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
     }
 }
 
@@ -537,12 +545,13 @@ extern "C" int cvb_attn_keys_supported(int H, int KV, int hd) {
 
 extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const void* pages, const int* block_tables,
                                   int table_width, const int* cu_seqlens, const int* positions, int S, int num_tiles, int H,
-                                  int KV, int hd, int page_size, int window, int keep_first, float scale, int num_pages,
+                                  int KV, int hd, int vd, int page_size, int window, int keep_first, float scale, int num_pages,
                                   int all_single, int splits, float* parts, int64_t parts_floats, int* err_flag,
                                   cudaStream_t stream) {
     if (num_tiles == 0 || S == 0) return CVB_OK;
     if (S < 0 || num_tiles < 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || window < 0 || keep_first < 0) return CVB_E_SIZE;
     if (!cvb_attn_keys_supported(H, KV, hd)) return CVB_E_UNSUPPORTED;
+    if (vd <= 0 || vd > hd || vd % 16 != 0) return CVB_E_UNSUPPORTED;
     if (q_stride < H * hd || q_stride % 8 != 0) return CVB_E_ALIGN;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return CVB_E_ALIGN;
     if (KV > 65535) return CVB_E_SIZE;
@@ -552,7 +561,7 @@ extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const 
     p.pages = static_cast<const __nv_bfloat16*>(pages);
     p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
     p.q_stride = q_stride; p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size;
-    p.window = window; p.keep_first = keep_first; p.num_pages = num_pages;
+    p.window = window; p.keep_first = keep_first; p.num_pages = num_pages; p.vd = vd;
     p.page_shift = -1;
     for (int sh = 0; sh < 31; ++sh)
         if ((1 << sh) == page_size) p.page_shift = sh;

@@ -538,12 +538,13 @@ def attn_keys_tiles(q_lens, num_heads: int, num_kv_heads: int) -> int:
 def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
                    positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int,
                    page_size: int, scale: float, window: int = 0, keep_first: int = 0, all_single: bool = False, splits: int = 1,
-                   scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                   scratch: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> torch.Tensor:
     """Attention of prompt portions and decoded tokens over pages [kv head, slot, head_dim] whose keys are also the
     values; `q` may be the packed output of a projection (rows of q.shape[1] elements, queries first).  `all_single`:
     every request brings exactly one token (a decode step): a block per (request, kv head) whose warps share out the key
     tiles among themselves; with `splits` > 1 that many blocks share them, through `scratch` (float32,
-    attn_keys_scratch_floats elements) and a merge kernel."""
+    attn_keys_scratch_floats elements) and a merge kernel.  `value_dim` (a multiple of 16): only the first value_dim elements
+    of a key are its value; out is [T, H * value_dim]."""
     _cuda(out, q, pages, block_tables, cu_seqlens, positions); _contig(out, q, pages, block_tables, cu_seqlens, positions)
     if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_keys_bf16 takes bf16 queries, pages and output")
@@ -555,7 +556,8 @@ def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, bloc
     _check(_attn_keys_lib().cvb_attn_keys_bf16(
         _ptr(out), _ptr(q), c_int(q.shape[1]), _ptr(pages), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
-        c_int(page_size), c_int(window), c_int(keep_first), c_float(scale), c_int(num_pages), c_int(1 if all_single else 0),
+        c_int(head_dim if value_dim is None else value_dim), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale),
+        c_int(num_pages), c_int(1 if all_single else 0),
         c_int(splits), _ptr(scratch), c_int64(scratch.numel() if scratch is not None else 0),
         _ptr(error_flag(q.device)), _stream()), "attn_keys_bf16", kernels=2 if all_single and splits > 1 else 1)
     return out

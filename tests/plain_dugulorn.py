@@ -145,6 +145,19 @@ def latent_keys(x, w, p, m, eps, positions, rnd=identity):
     return c, kr
 
 
+def causal_attention(q_nope, q_rope, k, kr, v, scale):
+    """q_nope, k [T, H, dn]; q_rope [T, H, dr]; kr [T, dr] (one for all heads); v [T, H, dv].  Token i sees every j <= i;
+    ordinary softmax.  Returns [T, H, dv]."""
+    T, H = q_nope.shape[0], q_nope.shape[1]
+    visible = torch.arange(T)[None, :] <= torch.arange(T)[:, None]
+    out = torch.zeros(T, H, v.shape[-1], dtype=F)
+    for h in range(H):
+        s = (q_nope[:, h] @ k[:, h].T + q_rope[:, h] @ kr.T) * scale
+        s = s.masked_fill(~visible, -math.inf)
+        out[:, h] = torch.softmax(s, dim=-1) @ v[:, h]
+    return out
+
+
 def latent_attention(x, w, p, m, eps, positions, keys, rnd=identity):
     T = x.shape[0]
     H, dn, dr, dv = int(m["heads"]), int(m["dim"]), int(m["rot_dim"]), int(m["vdim"])
@@ -156,14 +169,21 @@ def latent_attention(x, w, p, m, eps, positions, keys, rnd=identity):
     k = (c @ w[p + "uk"].T).reshape(T, H, dn)
     v = (c @ w[p + "uv"].T).reshape(T, H, dv)
     gate = logistic(rnd(xr @ w[p + "g"].T))                               # [T, H]
-    visible = positions[None, :] <= positions[:, None]
-    out = torch.zeros(T, H, dv, dtype=F)
-    for h in range(H):
-        s = (q_nope[:, h] @ k[:, h].T + q_rope[:, h] @ kr.T) * float(m["scale"])
-        s = s.masked_fill(~visible, -math.inf)
-        a = torch.softmax(s, dim=-1)
-        out[:, h] = (a @ v[:, h]) * gate[:, h:h + 1]
+    out = causal_attention(q_nope, q_rope, k, kr, v, float(m["scale"])) * gate[:, :, None]
     return rnd(rnd(out.reshape(T, H * dv)) @ w[p + "o"].T)
+
+
+def lightning_rule(q, k, v, decays):
+    """q, k [T, H, dk], v [T, H, dv]: per head S <- d S + k v^T, o = S^T q, from S = 0.  Returns o [T, H, dv]."""
+    T, H, dk = q.shape
+    dv = v.shape[-1]
+    o = torch.zeros(T, H, dv, dtype=F)
+    for h in range(H):
+        S = torch.zeros(dk, dv, dtype=F)
+        for t in range(T):
+            S = float(decays[h]) * S + torch.outer(k[t, h], v[t, h])
+            o[t, h] = S.T @ q[t, h]
+    return o
 
 
 def lightning(x, w, p, m, eps, rnd=identity):
@@ -173,13 +193,7 @@ def lightning(x, w, p, m, eps, rnd=identity):
     q = silu(rnd(xr @ w[p + "q"].T)).reshape(T, H, dk)
     k = silu(rnd(xr @ w[p + "k"].T)).reshape(T, H, dk)
     v = silu(rnd(xr @ w[p + "v"].T)).reshape(T, H, dv)
-    o = torch.zeros(T, H, dv, dtype=F)
-    for h in range(H):
-        S = torch.zeros(dk, dv, dtype=F)
-        d = float(m["decay"][h])
-        for t in range(T):
-            S = d * S + torch.outer(k[t, h], v[t, h])
-            o[t, h] = S.T @ q[t, h]
+    o = lightning_rule(q, k, v, m["decay"])
     y = norm_plain(o.reshape(T, H * dv), w[p + "norm"], eps) * logistic(rnd(xr @ w[p + "g"].T))
     return rnd(rnd(y) @ w[p + "o"].T)
 
@@ -195,19 +209,19 @@ def causal_conv(u: torch.Tensor, taps: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def channel_delta(x, w, p, m, eps, rnd=identity):
-    T = x.shape[0]
-    H, G, dk, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
-    xr = rnd(x)
-    q = silu(causal_conv(rnd(xr @ w[p + "q"].T), w[p + "q.conv"])).reshape(T, G, dk)
-    k = silu(causal_conv(rnd(xr @ w[p + "k"].T), w[p + "k.conv"])).reshape(T, G, dk)
-    v = silu(causal_conv(rnd(xr @ w[p + "v"].T), w[p + "v.conv"])).reshape(T, H, dv)
-    q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * dk ** -0.5
-    k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
-    beta = logistic(xr @ w[p + "b"].T)                                    # [T, H]
-    a = rnd(rnd(xr @ w[p + "a1"].T)) @ w[p + "a2"].T + w[p + "dt_bias"]
-    soft = torch.where(a > 30, a, torch.log1p(torch.exp(torch.clamp(a, max=30.0))))
-    g = torch.exp(-torch.exp(w[p + "A_log"])[None, :, None] * soft.reshape(T, H, dk))      # [T, H, dk]
+def unit_vectors(x):
+    return x / torch.sqrt((x * x).sum(-1, keepdim=True) + 1e-6)
+
+
+def softplus(a):
+    return torch.where(a > 30, a, torch.log1p(torch.exp(torch.clamp(a, max=30.0))))
+
+
+def delta_rule(q, k, v, g, beta):
+    """q, k [T, G, dk], v [T, H, dv], g [T, H, dk], beta [T, H]: per head (reading q/k head h // (H / G)), from S = 0:
+    S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.  Returns o [T, H, dv]."""
+    T, G, dk = q.shape
+    H, dv = v.shape[1], v.shape[2]
     o = torch.zeros(T, H, dv, dtype=F)
     for h in range(H):
         kv = h // (H // G)
@@ -217,6 +231,22 @@ def channel_delta(x, w, p, m, eps, rnd=identity):
             u = beta[t, h] * (v[t, h] - S.T @ k[t, kv])
             S = S + torch.outer(k[t, kv], u)
             o[t, h] = S.T @ q[t, kv]
+    return o
+
+
+def channel_delta(x, w, p, m, eps, rnd=identity):
+    T = x.shape[0]
+    H, G, dk, dv = int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
+    xr = rnd(x)
+    q = silu(causal_conv(rnd(xr @ w[p + "q"].T), w[p + "q.conv"])).reshape(T, G, dk)
+    k = silu(causal_conv(rnd(xr @ w[p + "k"].T), w[p + "k.conv"])).reshape(T, G, dk)
+    v = silu(causal_conv(rnd(xr @ w[p + "v"].T), w[p + "v.conv"])).reshape(T, H, dv)
+    q = unit_vectors(q) * dk ** -0.5
+    k = unit_vectors(k)
+    beta = logistic(xr @ w[p + "b"].T)                                    # [T, H]
+    a = rnd(rnd(xr @ w[p + "a1"].T)) @ w[p + "a2"].T + w[p + "dt_bias"]
+    g = torch.exp(-torch.exp(w[p + "A_log"])[None, :, None] * softplus(a).reshape(T, H, dk))      # [T, H, dk]
+    o = delta_rule(q, k, v, g, beta)
     gate = logistic(rnd(rnd(rnd(xr @ w[p + "g1"].T)) @ w[p + "g2"].T)).reshape(T, H, dv)
     y = norm_plain(o, w[p + "norm"], eps) * gate
     return rnd(rnd(y.reshape(T, H * dv)) @ w[p + "o"].T)
