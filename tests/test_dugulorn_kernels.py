@@ -150,7 +150,7 @@ def _attention_case(dtype, H, R, dr, page, kernel, seed):
     q = _rand(T, H, HD, seed=seed + 9)
     # (request, row within the step's tokens of that request, head, key position): the query points at that key, strongly
     picks = [(0, 0, 0, 0), (0, 69, 1 % H, 199), (0, 35, 2 % H, page - 1), (0, 36, 0, page), (0, 10, H - 1, 127), (0, 11, 0, 128),
-             (0, 69, 0, 3), (1, 0, 0, 150), (1, 0, 1 % H, 0), (1, 0, H - 1, 4 * page - 1), (1, 0, 2 % H, 4 * page)]
+             (0, 69, 0, 3), (1, 0, 0, 150), (1, 0, 1 % H, 0), (1, 0, H - 1, 2 * page - 1), (1, 0, 2 % H, 2 * page)]
     base = [0, 70]
     picks = list({(r, row, h): (r, row, h, j) for r, row, h, j in reversed(picks)}.values())      # one key per (row, head)
     for r, row, h, j in picks:
