@@ -187,9 +187,16 @@ def _attention_case(dtype, H, R, dr, page, kernel, seed):
             s = (qr[base[r] + row] @ kk[:p + 1].T) * 0.25                    # [H, p + 1]
             ref = torch.softmax(s, dim=-1) @ kk[:p + 1, :R]
             worst = max(worst, float((got[base[r] + row] - ref).abs().max()))
+    found = 0
     for r, row, h, j in picks:                                                # the pointed-at key is what comes out
-        ref = keys[r][j].to(dtype).to(F64)[:R]
-        assert float((got[base[r] + row, h] - ref).abs().max()) < 0.05 * float(ref.abs().max()) + 0.02, (r, row, h, j)
+        kk = keys[r].to(dtype).to(F64)
+        p = q_of[r][row]
+        weight = torch.softmax((qr[base[r] + row, h] @ kk[:p + 1].T) * 0.25, dim=-1)[j]
+        if float(weight) > 0.99:                                              # (with few elements another key may lie as close)
+            found += 1
+            ref = kk[j, :R]
+            assert float((got[base[r] + row, h] - ref).abs().max()) < 0.05 * float(ref.abs().max()) + 0.02, (r, row, h, j)
+    assert found >= len(picks) - 3
     assert worst < (1e-5 if dtype == torch.float32 else 3e-2), worst
 
 
