@@ -146,6 +146,7 @@ def _attention_case(dtype, H, R, dr, page, kernel, seed):
     g = torch.Generator().manual_seed(seed)
     order = torch.randperm(n_pages, generator=g).tolist()
     keys = [_rand(n, HD, seed=seed + 1 + i) for i, n in enumerate(lens)]
+    keys = [k / k.norm(dim=-1, keepdim=True) * math.sqrt(HD) for k in keys]      # equal lengths: no other key scores higher than the one pointed at
     T = sum(len(x) for x in q_of)
     q = _rand(T, H, HD, seed=seed + 9)
     # (request, row within the step's tokens of that request, head, key position): the query points at that key, strongly
@@ -154,7 +155,7 @@ def _attention_case(dtype, H, R, dr, page, kernel, seed):
     base = [0, 70]
     picks = list({(r, row, h): (r, row, h, j) for r, row, h, j in reversed(picks)}.values())      # one key per (row, head)
     for r, row, h, j in picks:
-        q[base[r] + row, h] = keys[r][j] * (40.0 / float(keys[r][j].norm() ** 2)) / 0.25
+        q[base[r] + row, h] = keys[r][j] * (100.0 / float(keys[r][j].norm() ** 2)) / 0.25
     pages = torch.full((n_pages, page, HD), float("nan"), dtype=dtype)      # what nobody owns holds NaN
     W = max((n + page - 1) // page for n in lens)
     tables = torch.full((2, W), -1, dtype=torch.int32)
@@ -196,7 +197,7 @@ def _attention_case(dtype, H, R, dr, page, kernel, seed):
             found += 1
             ref = kk[j, :R]
             assert float((got[base[r] + row, h] - ref).abs().max()) < 0.05 * float(ref.abs().max()) + 0.02, (r, row, h, j)
-    assert found >= len(picks) - 3
+    assert found >= len(picks) - 1
     assert worst < (1e-5 if dtype == torch.float32 else 3e-2), worst
 
 
