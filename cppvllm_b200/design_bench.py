@@ -1,4 +1,4 @@
-"""Givirax beside Qwen3 at equal layer sizes, random weights, bf16: prefill and decode throughput of whole models through
+"""A design beside Qwen3 at equal layer sizes (Givirax, below; Dugulorn, at the end of this text), random weights, bf16: prefill and decode throughput of whole models through
 the step function, and every kernel of the Givirax parts beside the like kernel of the Qwen3 parts, each with its
 fraction of its own roofline (bytes it must move over the measured copy bandwidth, or flops over the measured bf16 peak).
 
@@ -10,6 +10,16 @@ heads and head size, a window of 1,024 positions with 4 kept first tokens, and a
 of the same inner size with 8 gated experts, 2 per token, of half that inner size each (the same flops per token as the
 dense gated feed-forward of Qwen3).  Timing: CUDA events around steps that are already warm, buffers rotated or larger
 than the L2 for single kernels.
+
+    python bench.py --design dugulorn
+
+The Dugulorn model of a size has the same width and inner size; its layers repeat the pattern [latent attention with a
+feed-forward, lightning, latent attention reading the first one's cache with a feed-forward, channel delta]: as many heads as
+Qwen3's query heads, latent entries of 96 + 32 elements (the largest the tensor-core kernel takes), matrices of dim x dim per
+head in the two recurrent mixers.  Its kernels are timed beside the Qwen3 kernels that do the like job: latent attention
+beside grouped-query attention (prompt and decode), the two scans beside prompt attention (both are the mixer's core over
+2,048 tokens) and, for decoded tokens, as bytes of state over the copy bandwidth, the norm behind a sublayer beside the
+fused add-and-norm, bias and squared relu beside SwiGLU.
 """
 from __future__ import annotations
 
@@ -39,6 +49,26 @@ def givirax_config(s, max_positions):
     layers = [{"type": "attention", "mixer": mixer, "mlp": dense if i % 2 == 0 else moe} for i in range(s["layers"])]
     return {"architecture": "Givirax", "vocab": s["vocab"], "width": s["width"], "max_positions": max_positions,
             "embedding": {"scale": math.sqrt(s["width"])}, "norm": {"eps": 1e-5}, "layers": layers}
+
+
+def dugulorn_config(s, max_positions):
+    D, H, hd = s["width"], s["heads"], s["dim"]
+    rot = {"dims": 32, "base": 250000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+
+    def latent(src=None):
+        m = {"heads": H, "dim": hd, "rot_dim": 32, "vdim": hd, "q_rank": 3 * D // 8, "kv_rank": 96, "scale": 1.0 / math.sqrt(hd + 32), "rot": rot}
+        if src is not None:
+            m["kv_from"] = src
+        return {"type": "latent_attention", "mixer": m, "mlp": {"kind": "dense", "ff": s["ff"]}}
+    layers = []
+    for i in range(0, s["layers"], 4):
+        layers += [latent(),
+                   {"type": "lightning", "mixer": {"heads": H, "dim": hd, "vdim": hd, "decay": [1.0 - 2.0 ** -(2 + 6 * h / H) for h in range(H)]}, "mlp": None},
+                   latent(i),
+                   {"type": "channel_delta", "mixer": {"heads": H, "kv_heads": s["kv_heads"], "dim": hd, "vdim": hd, "conv": 4, "a_rank": 64, "g_rank": 64},
+                    "mlp": None}]
+    return {"architecture": "Dugulorn", "vocab": s["vocab"], "width": D, "max_positions": max_positions, "norm": {"eps": 1e-5},
+            "layers": layers[:s["layers"]]}
 
 
 def qwen3_config(s, max_positions):
@@ -114,6 +144,7 @@ def model_points(cfg, prefill_tokens, batch, context, steps):
             nbytes = r.model.decode_weight_bytes() + sum(
                 b * min(context, (cs.window + cs.keep_first) if cs.window else context) * cs.elements_per_token() * 2 * len(m)
                 for cs, m in r.group_specs)
+            nbytes += sum(b * st[0].numel() * st.element_size() * 2 for st in r.states.values())      # per-request state: read and written
             out[f"decode_b{b}_tok_s"] = round(b / (ms / 1e3), 1)
             out[f"decode_b{b}_ms"] = round(ms, 4)
             out[f"decode_b{b}_hbm_frac"] = round(nbytes / (ms / 1e3) / 1e9 / peaks()["hbm_gbs"], 4)
@@ -269,9 +300,137 @@ def kernel_pairs(s, pk):
     return out
 
 
+def dugulorn_kernel_pairs(s, pk):
+    """The kernels that the Dugulorn parts brought, each beside the Qwen3 kernel that does the like job at the same sizes."""
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(0)
+    bf, f32 = torch.bfloat16, torch.float32
+    D, H, KV, hd, I = s["width"], s["heads"], s["kv_heads"], s["dim"], s["ff"]
+    R, dr = 96, 32
+    HD = R + dr
+    page, out = 32, {}
+
+    def rnd(*shape, scale=1.0, dtype=bf):
+        return (torch.randn(*shape, generator=g, device=d, dtype=f32) * scale).to(dtype)
+
+    def pair(name, new_us, new_work, like_us, like_work, unit, note=None):
+        peak = pk["hbm_gbs"] * 1e9 if unit == "bytes" else pk["bf16_tflops"] * 1e12
+        fn, fl = new_work / (new_us * 1e-6) / peak, like_work / (like_us * 1e-6) / peak
+        out[name] = {"new_us": round(new_us, 2), "new_frac": round(fn, 4), "like_us": round(like_us, 2), "like_frac": round(fl, 4),
+                     "gap": round(fl / fn, 2), "roofline": "copy bandwidth" if unit == "bytes" else "bf16 peak"}
+        if note:
+            out[name]["note"] = note
+
+    # -- attention of a prompt of 2,048 tokens ---------------------------------------------------------------------------
+    T = 2048
+    n_pages = T // page
+    pairs_seen = T * (T + 1) / 2
+    tables = torch.arange(n_pages, dtype=torch.int32, device=d).view(1, n_pages)
+    cu = torch.tensor([0, T], dtype=torch.int32, device=d)
+    pos = torch.arange(T, dtype=torch.int32, device=d)
+    lat_pages = rnd(n_pages + 1, page, HD)
+    q_lat = rnd(T, H * HD)
+    o_lat = torch.empty(T, H * R, dtype=bf, device=d)
+    tiles = ops.attn_keys_tiles([T], H, 1)
+    new = _us(lambda i: ops.attn_keys_bf16(o_lat, q_lat, lat_pages, tables, cu, pos, 1, tiles, H, 1, HD, page, 0.09, value_dim=R))
+    kv_pages = rnd(n_pages + 1, 2, KV, page, hd)
+    q = rnd(T, H * hd)
+    att = torch.empty(T, H * hd, dtype=bf, device=d)
+    tiles_tc = ops.prefill_tiles_tcgen05([T], H, KV)
+    like = _us(lambda i: ops.attn_prefill_tcgen05(att, q, kv_pages, tables, cu, pos, 1, tiles_tc, H, KV, hd, page, 0.09))
+    pair("attention_prefill_2048", new, 2.0 * H * (HD + R) * pairs_seen, like, 4.0 * H * hd * pairs_seen, "flops")
+
+    # -- attention of decoded tokens: batch 8 at 4,096 tokens --------------------------------------------------------------
+    B, ctx = 8, 4096
+    pps = ctx // page
+    copies = 8
+    tabs = [torch.randperm(B * pps, generator=g, device=d).to(torch.int32).view(B, pps).contiguous() for _ in range(copies)]
+    lat_big = [rnd(B * pps + 1, page, HD) for _ in range(copies)]
+    kv_big = [rnd(B * pps + 1, 2, KV, page, hd) for _ in range(copies)]
+    cu_b = torch.arange(0, B + 1, dtype=torch.int32, device=d)
+    pos_b = torch.full((B,), ctx - 1, dtype=torch.int32, device=d)
+    ql_b, q_b = rnd(B, H * HD), rnd(B, H * hd)
+    ol_b, att_b = torch.empty(B, H * R, dtype=bf, device=d), torch.empty(B, H * hd, dtype=bf, device=d)
+    single = H <= 16
+    z = ops.attn_keys_decode_splits(B, 1, ctx) if single else 1
+    parts = torch.empty(max(1, ops.attn_keys_scratch_floats(B, 1, HD, z)), dtype=f32, device=d)
+    new = _us(lambda i: ops.attn_keys_bf16(ol_b, ql_b, lat_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B if single else ops.attn_keys_tiles([1] * B, H, 1),
+                                           H, 1, HD, page, 0.09, all_single=single, splits=z, scratch=parts if z > 1 else None, value_dim=R))
+    splits = 4
+    scratch = torch.empty(max(1, ops.attn_decode_scratch_floats(B, KV, hd, splits)), dtype=f32, device=d)
+    like = _us(lambda i: ops.attn_decode_bf16(att_b, q_b, kv_big[i % copies], tabs[i % copies], cu_b, pos_b, B, H, KV, hd, page, 0.09,
+                                              splits, scratch))
+    pair("attention_decode_b8_ctx_4096", new, B * ctx * HD * 2.0, like, B * ctx * KV * hd * 4.0, "bytes")
+    del lat_big, kv_big
+
+    # -- the two scans over a prompt of 2,048 tokens, beside prompt attention (the mixer's core in both designs) -----------
+    slots = torch.zeros(1, dtype=torch.int32, device=d)
+    state = torch.zeros(2, H * hd * hd + 3 * (2 * KV * hd + H * hd), dtype=f32, device=d)
+    packed = rnd(T, 4 * H * hd)
+    o32 = torch.empty(T, H * hd, dtype=f32, device=d)
+    decay = torch.full((H,), 0.99, dtype=f32, device=d)
+    new = _us(lambda i: ops.lightning_scan(o32, packed, 0, H * hd, 2 * H * hd, state, decay, cu, slots, 1, H, hd, hd))
+    attn_us = out["attention_prefill_2048"]["like_us"]
+    out["lightning_prefill_2048"] = {"new_us": round(new, 2), "new_frac": round(4.0 * H * hd * hd * T / (new * 1e-6) / (pk["bf16_tflops"] * 1e12), 5),
+                                     "like_us": attn_us, "like_frac": out["attention_prefill_2048"]["like_frac"],
+                                     "roofline": "bf16 peak (a token-by-token scan on the float units cannot come near it)"}
+    qn, kn = rnd(T, KV * hd, dtype=f32), rnd(T, KV * hd, dtype=f32)
+    vv, gg, bb = rnd(T, H * hd, dtype=f32), torch.rand(T, H * hd, generator=g, device=d), torch.rand(T, H, generator=g, device=d)
+    new = _us(lambda i: ops.delta_scan(o32, qn, kn, vv, gg, bb, state, cu, slots, 1, H, KV, hd, hd))
+    out["delta_prefill_2048"] = {"new_us": round(new, 2), "new_frac": round(6.0 * H * hd * hd * T / (new * 1e-6) / (pk["bf16_tflops"] * 1e12), 5),
+                                 "like_us": attn_us, "like_frac": out["attention_prefill_2048"]["like_frac"],
+                                 "roofline": "bf16 peak (a token-by-token scan on the float units cannot come near it)"}
+    C = 2 * KV * hd + H * hd
+    raw, conv_w = rnd(T, C), rnd(C, 4, dtype=f32)
+    a32, b32 = rnd(T, H * hd, dtype=f32), rnd(T, H, dtype=f32)
+    dt, alog = rnd(H * hd, dtype=f32), rnd(H, dtype=f32)
+    seq_of = torch.zeros(T, dtype=torch.int32, device=d)
+    new = _us(lambda i: ops.delta_prep(qn, kn, vv, gg, bb, raw, 0, conv_w, a32, dt, alog, b32, state, H * hd * hd, seq_of, cu, slots, H, KV, hd, hd))
+    out["delta_prep_2048"] = {"new_us": round(new, 2), "new_frac": round(T * (C * 2 + H * hd * 4 + (2 * KV * hd + 2 * H * hd) * 4.0) / (new * 1e-6) / (pk["hbm_gbs"] * 1e9), 4),
+                              "roofline": "copy bandwidth", "note": "no like kernel in the closest model"}
+
+    # -- the scans of 8 decoded tokens: the state is read and written once -------------------------------------------------
+    Bs = 8
+    n_copy = max(2, int(300e6 // (Bs * H * hd * hd * 4)) + 1)
+    states = [torch.zeros(Bs + 1, H * hd * hd, dtype=f32, device=d) for _ in range(n_copy)]
+    cu8, slots8 = torch.arange(0, Bs + 1, dtype=torch.int32, device=d), torch.arange(0, Bs, dtype=torch.int32, device=d)
+    new = _us(lambda i: ops.lightning_scan(o32[:Bs], packed[:Bs], 0, H * hd, 2 * H * hd, states[i % n_copy], decay, cu8, slots8, Bs, H, hd, hd))
+    like_d = out["attention_decode_b8_ctx_4096"]
+    out["lightning_decode_b8"] = {"new_us": round(new, 2), "new_frac": round(Bs * H * hd * hd * 8.0 / (new * 1e-6) / (pk["hbm_gbs"] * 1e9), 4),
+                                  "like_us": like_d["like_us"], "like_frac": like_d["like_frac"], "roofline": "copy bandwidth"}
+    new = _us(lambda i: ops.delta_scan(o32[:Bs], qn[:Bs], kn[:Bs], vv[:Bs], gg[:Bs], bb[:Bs], states[i % n_copy], cu8, slots8, Bs, H, KV, hd, hd))
+    out["delta_decode_b8"] = {"new_us": round(new, 2), "new_frac": round(Bs * H * hd * hd * 8.0 / (new * 1e-6) / (pk["hbm_gbs"] * 1e9), 4),
+                              "like_us": like_d["like_us"], "like_frac": like_d["like_frac"], "roofline": "copy bandwidth"}
+    for k in ("lightning_decode_b8", "delta_decode_b8"):
+        out[k]["gap"] = round(out[k]["like_frac"] / out[k]["new_frac"], 2)
+    del states
+
+    # -- elementwise kernels, 2,048 tokens -------------------------------------------------------------------------------------
+    h32 = torch.randn(T, D, generator=g, device=d)
+    y, copy = rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
+    w, bias = torch.ones(D, device=d), torch.zeros(D, device=d)
+    new = _us(lambda i: ops.norm_add(h32, y, w, 1e-5, bias=bias, copy=copy))
+    h16, normed = rnd(T, D), torch.empty(T, D, dtype=bf, device=d)
+    like = _us(lambda i: ops.add_rmsnorm(normed, h16, y, w, 1e-6))
+    pair("norm_behind_sublayer_2048_tokens", new, T * D * (4 + 4 + 2 + 2.0), like, T * D * (2 + 2 + 2 + 2.0), "bytes")
+    up, bup = rnd(T, I), torch.zeros(I, device=d)
+    new = _us(lambda i: ops.bias_act(up, up, bup, "relu2"))
+    gu_t, act = rnd(T, 2 * I), torch.empty(T, I, dtype=bf, device=d)
+    like = _us(lambda i: ops.swiglu(act, gu_t))
+    pair("activation_2048_tokens", new, T * I * 4.0, like, T * I * 6.0, "bytes")
+    o_rows, gate = torch.randn(T, H * hd, generator=g, device=d), rnd(T, H * hd)
+    yy = torch.empty(T, H * hd, dtype=bf, device=d)
+    wn = torch.ones(hd, device=d)
+    new = _us(lambda i: ops.gated_norm(yy, o_rows, gate, wn, H, 1e-5))
+    out["gated_norm_2048_tokens"] = {"new_us": round(new, 2), "new_frac": round(T * H * hd * 8.0 / (new * 1e-6) / (pk["hbm_gbs"] * 1e9), 4),
+                                     "roofline": "copy bandwidth", "note": "no like kernel in the closest model"}
+    return out
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="design_bench", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--design", default="givirax", choices=["givirax"])
+    ap.add_argument("--design", default="givirax", choices=["givirax", "dugulorn"])
     ap.add_argument("--sizes", default="small,large")
     ap.add_argument("--steps", type=int, default=48)
     ap.add_argument("--no-kernels", action="store_true", help="whole models only")
@@ -283,18 +442,20 @@ def main(argv=None) -> int:
     from .csrc import ops
     ops.configure_library_matmul()
     pk = peaks()
-    result = {"design": a.design, "closest": "Qwen3ForCausalLM", "dtype": "bf16", "data": "synthetic, random weights", "peaks": pk,
-              "window": WINDOW, "keep_first": KEEP, "experts": EXPERTS, "top": TOP, "sizes": {}}
+    result = {"design": a.design, "closest": "Qwen3ForCausalLM", "dtype": "bf16", "data": "synthetic, random weights", "peaks": pk, "sizes": {}}
+    if a.design == "givirax":
+        result.update(window=WINDOW, keep_first=KEEP, experts=EXPERTS, top=TOP)
     for name in a.sizes.split(","):
         s = SIZES[name]
         entry = {"shape": s}
         if not a.no_models:
             t0 = time.time()
-            entry["givirax"] = model_points(givirax_config(s, 4160), 2048, 8, 4096, a.steps)
+            design_config = givirax_config if a.design == "givirax" else dugulorn_config
+            entry[a.design] = model_points(design_config(s, 4160), 2048, 8, 4096, a.steps)
             entry["qwen3"] = model_points(qwen3_config(s, 4160), 2048, 8, 4096, a.steps)
             entry["seconds"] = round(time.time() - t0, 1)
         if not a.no_kernels:
-            entry["kernels"] = kernel_pairs(s, pk)
+            entry["kernels"] = kernel_pairs(s, pk) if a.design == "givirax" else dugulorn_kernel_pairs(s, pk)
         result["sizes"][name] = entry
     print(json.dumps(result))
     return 0
