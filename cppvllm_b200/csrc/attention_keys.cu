@@ -34,6 +34,8 @@ struct KeysAttnParams {
     const int* positions;               // [T]
     int q_stride, table_width, S, H, KV, page_size, window, keep_first, num_pages;
     int vd;                             // leading elements of a key that are its value (HD: all of them)
+    int kv_phys;                        // kv heads the pages hold; KV (the heads the grid walks) is a multiple of it: the
+                                        // query heads of one stored kv head may be dealt with as several groups
     int page_shift;                     // log2(page_size) if that is a power of two, else -1
     // decode form only: the key tiles of a (request, kv head) are shared out among `splits` blocks (gridDim.z); with more
     // than one, a block leaves its part (unnormalised rows, maxima, sums) in `parts` and a second kernel merges them
@@ -130,7 +132,7 @@ attn_keys_kernel(const KeysAttnParams p) {
                     atomicExch(p.err, 4);                 // a key a token of this block must see has no page
                     need = false;
                 } else {
-                    src = p.pages + ((static_cast<int64_t>(page) * p.KV + kvh) * p.page_size + off) * HD + c * 8;
+                    src = p.pages + ((static_cast<int64_t>(page) * p.kv_phys + kvh / (p.KV / p.kv_phys)) * p.page_size + off) * HD + c * 8;
                 }
             }
             cp_async16(dst + r * LD + c * 8, src, need);
@@ -331,7 +333,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
                 if (slot != last_slot) {
                     page = slot < p.table_width ? table[slot] : -1;
                     last_slot = slot;
-                    page_base = p.pages + (static_cast<int64_t>(page) * p.KV + kvh) * p.page_size * HD;
+                    page_base = p.pages + (static_cast<int64_t>(page) * p.kv_phys + kvh / (p.KV / p.kv_phys)) * p.page_size * HD;
                 }
                 if (page < 0 || page >= p.num_pages) {
                     atomicExch(p.err, 4);
@@ -546,12 +548,14 @@ extern "C" int cvb_attn_keys_supported(int H, int KV, int hd) {
 extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const void* pages, const int* block_tables,
                                   int table_width, const int* cu_seqlens, const int* positions, int S, int num_tiles, int H,
                                   int KV, int hd, int vd, int page_size, int window, int keep_first, float scale, int num_pages,
-                                  int all_single, int splits, float* parts, int64_t parts_floats, int* err_flag,
+                                  int all_single, int splits, float* parts, int64_t parts_floats, int kv_phys, int* err_flag,
                                   cudaStream_t stream) {
     if (num_tiles == 0 || S == 0) return CVB_OK;
     if (S < 0 || num_tiles < 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0 || window < 0 || keep_first < 0) return CVB_E_SIZE;
     if (!cvb_attn_keys_supported(H, KV, hd)) return CVB_E_UNSUPPORTED;
     if (vd <= 0 || vd > hd || vd % 16 != 0) return CVB_E_UNSUPPORTED;
+    if (kv_phys <= 0) kv_phys = KV;
+    if (KV % kv_phys != 0) return CVB_E_SHAPE;
     if (q_stride < H * hd || q_stride % 8 != 0) return CVB_E_ALIGN;
     if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(pages) | reinterpret_cast<uintptr_t>(out)) & 15) return CVB_E_ALIGN;
     if (KV > 65535) return CVB_E_SIZE;
@@ -561,7 +565,7 @@ extern "C" int cvb_attn_keys_bf16(void* out, const void* q, int q_stride, const 
     p.pages = static_cast<const __nv_bfloat16*>(pages);
     p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
     p.q_stride = q_stride; p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size;
-    p.window = window; p.keep_first = keep_first; p.num_pages = num_pages; p.vd = vd;
+    p.window = window; p.keep_first = keep_first; p.num_pages = num_pages; p.vd = vd; p.kv_phys = kv_phys;
     p.page_shift = -1;
     for (int sh = 0; sh < 31; ++sh)
         if ((1 << sh) == page_size) p.page_shift = sh;

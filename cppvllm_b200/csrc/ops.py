@@ -418,7 +418,7 @@ def _recurrent_lib():
     global _recurrent
     if _recurrent is None:
         lib = load_library("recurrent")
-        for name in ("cvb_lightning_scan", "cvb_delta_prep", "cvb_conv_history", "cvb_delta_scan"):
+        for name in ("cvb_lightning_prep", "cvb_lightning_scan", "cvb_delta_prep", "cvb_conv_history", "cvb_delta_scan"):
             getattr(lib, name).restype = c_int
         _recurrent = lib
     return _recurrent
@@ -430,19 +430,34 @@ def _state_args(state: torch.Tensor):
     return _ptr(state), c_int64(state.shape[1]), state.shape[0]
 
 
-def lightning_scan(out: torch.Tensor, packed: torch.Tensor, q_off: int, k_off: int, v_off: int, state: torch.Tensor, decay: torch.Tensor,
+def lightning_prep(qf: torch.Tensor, kf: torch.Tensor, vf: torch.Tensor, packed: torch.Tensor, q_off: int, k_off: int, v_off: int) -> None:
+    """qf, kf [T, H * dim] and vf [T, H * vdim] (float32) = silu of the packed projection's column ranges from q_off, k_off, v_off."""
+    _cuda(qf, kf, vf, packed); _contig(qf, kf, vf, packed)
+    T = packed.shape[0]
+    if (qf.dtype != torch.float32 or kf.dtype != torch.float32 or vf.dtype != torch.float32 or qf.shape != kf.shape
+            or qf.shape[0] != T or vf.shape[0] != T):
+        raise KernelError("lightning_prep: qf, kf [T, H * dim] and vf [T, H * vdim] are float32")
+    _check(_recurrent_lib().cvb_lightning_prep(_ptr(qf), _ptr(kf), _ptr(vf), _ptr(packed), c_int(T), c_int(packed.shape[1]), c_int(q_off),
+                                               c_int(k_off), c_int(v_off), c_int(qf.shape[1]), c_int(vf.shape[1]),
+                                               c_int(dtype_code(packed.dtype)), _stream()), "lightning_prep")
+
+
+def lightning_scan(out: torch.Tensor, qf: torch.Tensor, kf: torch.Tensor, vf: torch.Tensor, state: torch.Tensor, decay: torch.Tensor,
                    cu_seqlens: torch.Tensor, state_slots: torch.Tensor, num_seqs: int, num_heads: int, dim: int, vdim: int) -> torch.Tensor:
-    """Per request and head, over the request's tokens of this step: S <- decay_h S + k v^T, out = S^T q with q, k, v = silu of
-    the packed projection's columns; S [dim, vdim] float32 at the front of the request's state row.  out float32 [T, H * vdim]."""
-    _cuda(out, packed, state, decay, cu_seqlens, state_slots); _contig(out, packed, decay, cu_seqlens, state_slots)
+    """Per request and head, over the request's tokens of this step: S <- decay_h S + k v^T, out = S^T q; q, k [T, H * dim] and
+    v [T, H * vdim] float32; S [dim, vdim] float32 at the front of the request's state row.  out float32 [T, H * vdim]."""
+    _cuda(out, qf, kf, vf, state, decay, cu_seqlens, state_slots); _contig(out, qf, kf, vf, decay, cu_seqlens, state_slots)
     sp, sf, n_slots = _state_args(state)
-    if (out.dtype != torch.float32 or out.shape != (packed.shape[0], num_heads * vdim) or decay.dtype != torch.float32
-            or decay.numel() != num_heads or cu_seqlens.dtype != torch.int32 or state_slots.dtype != torch.int32):
-        raise KernelError("lightning_scan: out float32 [T, H * vdim]; decay float32 [H]; cu_seqlens, state_slots int32")
+    T = qf.shape[0]
+    if (out.dtype != torch.float32 or out.shape != (T, num_heads * vdim) or decay.dtype != torch.float32 or decay.numel() != num_heads
+            or cu_seqlens.dtype != torch.int32 or state_slots.dtype != torch.int32 or qf.dtype != torch.float32
+            or kf.dtype != torch.float32 or vf.dtype != torch.float32 or qf.shape != (T, num_heads * dim) or kf.shape != qf.shape
+            or vf.shape != out.shape):
+        raise KernelError("lightning_scan: q, k float32 [T, H * dim]; v, out float32 [T, H * vdim]; decay float32 [H]; cu_seqlens, "
+                          "state_slots int32")
     _check(_recurrent_lib().cvb_lightning_scan(
-        _ptr(out), _ptr(packed), c_int(packed.shape[1]), c_int(q_off), c_int(k_off), c_int(v_off), sp, sf, _ptr(decay), _ptr(cu_seqlens),
-        _ptr(state_slots), c_int(n_slots), c_int(num_seqs), c_int(num_heads), c_int(dim), c_int(vdim), c_int(dtype_code(packed.dtype)),
-        _ptr(error_flag(out.device)), _stream()), "lightning_scan")
+        _ptr(out), _ptr(qf), _ptr(kf), _ptr(vf), sp, sf, _ptr(decay), _ptr(cu_seqlens), _ptr(state_slots), c_int(n_slots), c_int(num_seqs),
+        c_int(num_heads), c_int(dim), c_int(vdim), _ptr(error_flag(out.device)), _stream()), "lightning_scan")
     return out
 
 
@@ -538,19 +553,21 @@ def attn_keys_tiles(q_lens, num_heads: int, num_kv_heads: int) -> int:
 def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, block_tables: torch.Tensor, cu_seqlens: torch.Tensor,
                    positions: torch.Tensor, num_seqs: int, num_tiles: int, num_heads: int, num_kv_heads: int, head_dim: int,
                    page_size: int, scale: float, window: int = 0, keep_first: int = 0, all_single: bool = False, splits: int = 1,
-                   scratch: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> torch.Tensor:
+                   scratch: Optional[torch.Tensor] = None, value_dim: Optional[int] = None, kv_heads_in_pages: int = 0) -> torch.Tensor:
     """Attention of prompt portions and decoded tokens over pages [kv head, slot, head_dim] whose keys are also the
     values; `q` may be the packed output of a projection (rows of q.shape[1] elements, queries first).  `all_single`:
     every request brings exactly one token (a decode step): a block per (request, kv head) whose warps share out the key
     tiles among themselves; with `splits` > 1 that many blocks share them, through `scratch` (float32,
     attn_keys_scratch_floats elements) and a merge kernel.  `value_dim` (a multiple of 16): only the first value_dim elements
-    of a key are its value; out is [T, H * value_dim]."""
+    of a key are its value; out is [T, H * value_dim].  `kv_heads_in_pages` (a divisor of num_kv_heads): the pages hold fewer
+    kv heads than the grid walks, the query heads of one stored head being dealt with as several groups (a decode step of more
+    than 16 query heads per stored head)."""
     _cuda(out, q, pages, block_tables, cu_seqlens, positions); _contig(out, q, pages, block_tables, cu_seqlens, positions)
     if q.dtype != torch.bfloat16 or pages.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
         raise KernelError("attn_keys_bf16 takes bf16 queries, pages and output")
     if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or cu_seqlens.dtype != torch.int32 or positions.dtype != torch.int32:
         raise KernelError("attn_keys_bf16: block_tables [S, W], cu_seqlens and positions must be int32")
-    num_pages = pages.numel() // (num_kv_heads * page_size * head_dim)
+    num_pages = pages.numel() // ((kv_heads_in_pages or num_kv_heads) * page_size * head_dim)
     if splits > 1 and (scratch is None or scratch.dtype != torch.float32 or not scratch.is_cuda or not scratch.is_contiguous()):
         raise KernelError("attn_keys_bf16: splits need a contiguous float32 CUDA scratch")
     _check(_attn_keys_lib().cvb_attn_keys_bf16(
@@ -558,7 +575,7 @@ def attn_keys_bf16(out: torch.Tensor, q: torch.Tensor, pages: torch.Tensor, bloc
         _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(head_dim if value_dim is None else value_dim), c_int(page_size), c_int(window), c_int(keep_first), c_float(scale),
         c_int(num_pages), c_int(1 if all_single else 0),
-        c_int(splits), _ptr(scratch), c_int64(scratch.numel() if scratch is not None else 0),
+        c_int(splits), _ptr(scratch), c_int64(scratch.numel() if scratch is not None else 0), c_int(kv_heads_in_pages),
         _ptr(error_flag(q.device)), _stream()), "attn_keys_bf16", kernels=2 if all_single and splits > 1 else 1)
     return out
 

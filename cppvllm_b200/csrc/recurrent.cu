@@ -1,6 +1,7 @@
 // Mixers that carry a matrix of fixed size per request and head from token to token instead of a cache that grows:
 //
-//   lightning_scan : q = silu(a_q), k = silu(a_k), v = silu(a_v) from a packed projection;  S <- d_h S + k v^T;  o = S^T q
+//   lightning_prep : q = silu(a_q), k = silu(a_k), v = silu(a_v) in float, from a packed projection
+//   lightning_scan : S <- d_h S + k v^T;  o = S^T q
 //   delta_prep     : per token, everything the delta rule needs, in float: short causal convolutions over time (per channel,
 //                    the last tap on the current token, history from the request's state where the portion begins) with
 //                    silu behind them; q and k made unit vectors per head (x / sqrt(sum x^2 + 1e-6); q also times
@@ -10,86 +11,170 @@
 //
 // S is [dk, dv] per (request, head), float, in the request's state slot; portions of any length continue where the
 // state stands, one token after the other in the same order of operations, so cutting a sequence changes no bit.
-// A block owns 32 columns of S of one (request, head); four lanes share a column (rows r * 4 + lane part) and add their
-// parts up by shuffles.  The tokens of a portion are staged through shared memory a few at a time.
+// A block owns 16 columns of S of one (request, head); eight lanes share a column and add their parts up by shuffles.  The
+// tokens of a portion travel through two stages of shared memory by cp.async.
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace cvb {
 
 constexpr int kScanThreads = 128;
-constexpr int kScanCols = 32;
-constexpr int kLightChunk = 16;
-constexpr int kDeltaChunk = 8;
+constexpr int kScanLanes = 8;                            // lanes that share a column of S
+constexpr int kScanCols = kScanThreads / kScanLanes;     // columns of S per block
+constexpr int kScanChunk = 8;                            // tokens per stage
 
 __device__ __forceinline__ float silu_of(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float sigmoid_of(float z) { return 1.f / (1.f + expf(-z)); }
 
-template <typename T, int KPT>
-__global__ void __launch_bounds__(kScanThreads)
-lightning_scan_kernel(float* __restrict__ out, const T* __restrict__ packed, int stride, int q_off, int k_off, int v_off,
-                      float* __restrict__ state, int64_t state_floats, const float* __restrict__ decay,
-                      const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int num_slots, int H, int dk, int dv,
-                      int* __restrict__ err) {
+__device__ __forceinline__ void cp_async4(void* smem, const void* gmem) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(smem_u32(smem)), "l"(gmem));
+}
+
+// q = silu(a_q), k = silu(a_k), v = silu(a_v) in float, from the column ranges of a packed projection.
+template <typename T>
+__global__ void lightning_prep_kernel(float* __restrict__ qf, float* __restrict__ kf, float* __restrict__ vf, const T* __restrict__ packed,
+                                      int stride, int q_off, int k_off, int v_off, int nqk, int nv, int64_t total) {
     pdl_trigger();
     pdl_wait();
-    extern __shared__ float sm[];
-    constexpr int dkp = KPT * 4;
-    float* qs = sm;                               // [chunk][dkp]
-    float* ks = qs + kLightChunk * dkp;           // [chunk][dkp]
-    float* vs = ks + kLightChunk * dkp;           // [chunk][32]
+    const int per = 2 * nqk + nv;
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t t = i / per;
+        const int c = static_cast<int>(i - t * per);
+        const T* row = packed + t * stride;
+        if (c < nqk) qf[t * nqk + c] = silu_of(to_float(row[q_off + c]));
+        else if (c < 2 * nqk) kf[t * nqk + c - nqk] = silu_of(to_float(row[k_off + c - nqk]));
+        else vf[t * nv + c - 2 * nqk] = silu_of(to_float(row[v_off + c - 2 * nqk]));
+    }
+}
+
+// The scan of both rules.  A block owns kScanCols columns of S of one (request, head); kScanLanes lanes share a column
+// (rows r * kScanLanes + lane part) and add their parts up by shuffles.  The tokens' q, k (and g), v (and b) travel through
+// two stages of shared memory by cp.async, kScanChunk tokens a stage, so that the next tokens arrive while these are used.
+// DELTA: S <- diag(g) S; u = b (v - S^T k); S <- S + k u^T; o = S^T q.   Else: S <- d S + k v^T; o = S^T q.
+template <int KPT, bool DELTA>
+__global__ void __launch_bounds__(kScanThreads)
+recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
+                      const float* __restrict__ gg, const float* __restrict__ bb, const float* __restrict__ decay,
+                      float* __restrict__ state, int64_t state_floats, const int* __restrict__ cu_seqlens,
+                      const int* __restrict__ state_slots, int num_slots, int H, int G, int dk, int dv, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
+    extern __shared__ __align__(16) float sm[];
+    constexpr int dkp = KPT * kScanLanes;
+    constexpr int kArrays = DELTA ? 3 : 2;
+    constexpr int kStage = kArrays * kScanChunk * dkp + kScanChunk * kScanCols + kScanChunk;
     const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * kScanCols;
-    const int tid = threadIdx.x, col = tid >> 2, part = tid & 3, j = j0 + col;
+    const int kvh = h / (H / G);
+    const int tid = threadIdx.x, col = tid / kScanLanes, part = tid % kScanLanes, j = j0 + col;
     const int begin = cu_seqlens[s], end = cu_seqlens[s + 1];
     const int slot = state_slots[s];
     if (slot < 0 || slot >= num_slots) {
         if (tid == 0) atomicExch(err, 2);
         return;
     }
+    for (int i = tid; i < 2 * kStage; i += kScanThreads) sm[i] = 0.f;       // the rows past dk stay zero for good
+    __syncthreads();
     float* st = state + static_cast<int64_t>(slot) * state_floats + static_cast<int64_t>(h) * dk * dv;
     float S[KPT];
 #pragma unroll
     for (int r = 0; r < KPT; ++r) {
-        const int i = r * 4 + part;
+        const int i = r * kScanLanes + part;
         S[r] = (i < dk && j < dv) ? st[static_cast<int64_t>(i) * dv + j] : 0.f;
     }
-    const float d = decay[h];
-    for (int t0 = begin; t0 < end; t0 += kLightChunk) {
-        const int n = min(kLightChunk, end - t0);
-        __syncthreads();
-        for (int idx = tid; idx < n * dkp; idx += kScanThreads) {
-            const int tt = idx / dkp, i = idx - tt * dkp;
-            float qv = 0.f, kv = 0.f;
-            if (i < dk) {
-                const T* row = packed + static_cast<int64_t>(t0 + tt) * stride;
-                qv = silu_of(to_float(row[q_off + h * dk + i]));
-                kv = silu_of(to_float(row[k_off + h * dk + i]));
+    const float d = DELTA ? 1.f : decay[h];
+    const bool vec = (dk & 3) == 0 && (dv & 3) == 0;
+
+    auto load = [&](int t0, int stage) {
+        const int n = min(kScanChunk, end - t0);
+        float* qs = sm + stage * kStage;
+        float* ks = qs + kScanChunk * dkp;
+        float* gs = ks + kScanChunk * dkp;                                  // DELTA only
+        float* vs = qs + kArrays * kScanChunk * dkp;
+        float* bs = vs + kScanChunk * kScanCols;
+        if (vec) {
+            const int dk4 = dk >> 2;
+            for (int idx = tid; idx < n * dk4; idx += kScanThreads) {
+                const int tt = idx / dk4, i = (idx - tt * dk4) * 4;
+                const int64_t tok = t0 + tt;
+                cp_async16(qs + tt * dkp + i, qn + (tok * G + kvh) * dk + i, true);
+                cp_async16(ks + tt * dkp + i, kn + (tok * G + kvh) * dk + i, true);
+                if (DELTA) cp_async16(gs + tt * dkp + i, gg + (tok * H + h) * dk + i, true);
             }
-            qs[idx] = qv;
-            ks[idx] = kv;
+            for (int idx = tid; idx < n * (kScanCols / 4); idx += kScanThreads) {
+                const int tt = idx / (kScanCols / 4), c = (idx - tt * (kScanCols / 4)) * 4;
+                if (j0 + c < dv) cp_async16(vs + tt * kScanCols + c, vv + (static_cast<int64_t>(t0 + tt) * H + h) * dv + j0 + c, true);
+            }
+        } else {
+            for (int idx = tid; idx < n * dk; idx += kScanThreads) {
+                const int tt = idx / dk, i = idx - tt * dk;
+                const int64_t tok = t0 + tt;
+                cp_async4(qs + tt * dkp + i, qn + (tok * G + kvh) * dk + i);
+                cp_async4(ks + tt * dkp + i, kn + (tok * G + kvh) * dk + i);
+                if (DELTA) cp_async4(gs + tt * dkp + i, gg + (tok * H + h) * dk + i);
+            }
+            for (int idx = tid; idx < n * kScanCols; idx += kScanThreads) {
+                const int tt = idx / kScanCols, c = idx - tt * kScanCols;
+                if (j0 + c < dv) cp_async4(vs + tt * kScanCols + c, vv + (static_cast<int64_t>(t0 + tt) * H + h) * dv + j0 + c);
+            }
         }
-        for (int idx = tid; idx < n * kScanCols; idx += kScanThreads) {
-            const int tt = idx / kScanCols, c = idx - tt * kScanCols;
-            vs[idx] = (j0 + c < dv) ? silu_of(to_float(packed[static_cast<int64_t>(t0 + tt) * stride + v_off + h * dv + j0 + c])) : 0.f;
-        }
+        if (DELTA && tid < n) cp_async4(bs + tid, bb + static_cast<int64_t>(t0 + tid) * H + h);
+    };
+
+    if (begin < end) load(begin, 0);
+    cp_async_commit();
+    int stage = 0;
+    for (int t0 = begin; t0 < end; t0 += kScanChunk, stage ^= 1) {
+        const int n = min(kScanChunk, end - t0);
+        if (t0 + kScanChunk < end) load(t0 + kScanChunk, stage ^ 1);
+        cp_async_commit();
+        cp_async_wait<1>();                                                  // everything but the newest group: this stage
         __syncthreads();
+        const float* qs = sm + stage * kStage;
+        const float* ks = qs + kScanChunk * dkp;
+        const float* gs = ks + kScanChunk * dkp;
+        const float* vs = qs + kArrays * kScanChunk * dkp;
+        const float* bs = vs + kScanChunk * kScanCols;
         for (int tt = 0; tt < n; ++tt) {
-            const float v = vs[tt * kScanCols + col];
             const float* kq = ks + tt * dkp + part;
             const float* qq = qs + tt * dkp + part;
-            float o = 0.f;
+            const float v = vs[tt * kScanCols + col];
+            float o0 = 0.f, o1 = 0.f;
+            if (DELTA) {
+                const float* gq = gs + tt * dkp + part;
+                float d0 = 0.f, d1 = 0.f;
 #pragma unroll
-            for (int r = 0; r < KPT; ++r) {
-                S[r] = fmaf(d, S[r], kq[r * 4] * v);
-                o = fmaf(S[r], qq[r * 4], o);
+                for (int r = 0; r < KPT; ++r) {
+                    S[r] *= gq[r * kScanLanes];
+                    if (r & 1) d1 = fmaf(S[r], kq[r * kScanLanes], d1); else d0 = fmaf(S[r], kq[r * kScanLanes], d0);
+                }
+                float dot = d0 + d1;
+#pragma unroll
+                for (int m = 1; m < kScanLanes; m <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, m);
+                const float u = bs[tt] * (v - dot);
+#pragma unroll
+                for (int r = 0; r < KPT; ++r) {
+                    S[r] = fmaf(kq[r * kScanLanes], u, S[r]);
+                    if (r & 1) o1 = fmaf(S[r], qq[r * kScanLanes], o1); else o0 = fmaf(S[r], qq[r * kScanLanes], o0);
+                }
+            } else {
+#pragma unroll
+                for (int r = 0; r < KPT; ++r) {
+                    S[r] = fmaf(d, S[r], kq[r * kScanLanes] * v);
+                    if (r & 1) o1 = fmaf(S[r], qq[r * kScanLanes], o1); else o0 = fmaf(S[r], qq[r * kScanLanes], o0);
+                }
             }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
+            float o = o0 + o1;
+#pragma unroll
+            for (int m = 1; m < kScanLanes; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
             if (part == 0 && j < dv) out[(static_cast<int64_t>(t0 + tt) * H + h) * dv + j] = o;
         }
+        __syncthreads();                                                     // the stage may be filled again
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int r = 0; r < KPT; ++r) {
-        const int i = r * 4 + part;
+        const int i = r * kScanLanes + part;
         if (i < dk && j < dv) st[static_cast<int64_t>(i) * dv + j] = S[r];
     }
 }
@@ -174,118 +259,64 @@ conv_history_kernel(float* __restrict__ state, int64_t state_floats, int64_t con
     }
 }
 
-template <int KPT>
-__global__ void __launch_bounds__(kScanThreads)
-delta_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ vv,
-                  const float* __restrict__ gg, const float* __restrict__ bb, float* __restrict__ state, int64_t state_floats,
-                  const int* __restrict__ cu_seqlens, const int* __restrict__ state_slots, int num_slots, int H, int G, int dk, int dv,
-                  int* __restrict__ err) {
-    pdl_trigger();
-    pdl_wait();
-    extern __shared__ float sm[];
-    constexpr int dkp = KPT * 4;
-    float* qs = sm;                               // [chunk][dkp]
-    float* ks = qs + kDeltaChunk * dkp;
-    float* gs = ks + kDeltaChunk * dkp;
-    float* vs = gs + kDeltaChunk * dkp;           // [chunk][32]
-    float* bs = vs + kDeltaChunk * kScanCols;     // [chunk]
-    const int s = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * kScanCols;
-    const int kvh = h / (H / G);
-    const int tid = threadIdx.x, col = tid >> 2, part = tid & 3, j = j0 + col;
-    const int begin = cu_seqlens[s], end = cu_seqlens[s + 1];
-    const int slot = state_slots[s];
-    if (slot < 0 || slot >= num_slots) {
-        if (tid == 0) atomicExch(err, 2);
-        return;
-    }
-    float* st = state + static_cast<int64_t>(slot) * state_floats + static_cast<int64_t>(h) * dk * dv;
-    float S[KPT];
-#pragma unroll
-    for (int r = 0; r < KPT; ++r) {
-        const int i = r * 4 + part;
-        S[r] = (i < dk && j < dv) ? st[static_cast<int64_t>(i) * dv + j] : 0.f;
-    }
-    for (int t0 = begin; t0 < end; t0 += kDeltaChunk) {
-        const int n = min(kDeltaChunk, end - t0);
-        __syncthreads();
-        for (int idx = tid; idx < n * dkp; idx += kScanThreads) {
-            const int tt = idx / dkp, i = idx - tt * dkp;
-            const int64_t tok = t0 + tt;
-            qs[idx] = i < dk ? qn[(tok * G + kvh) * dk + i] : 0.f;
-            ks[idx] = i < dk ? kn[(tok * G + kvh) * dk + i] : 0.f;
-            gs[idx] = i < dk ? gg[(tok * H + h) * dk + i] : 0.f;
-        }
-        for (int idx = tid; idx < n * kScanCols; idx += kScanThreads) {
-            const int tt = idx / kScanCols, c = idx - tt * kScanCols;
-            vs[idx] = (j0 + c < dv) ? vv[(static_cast<int64_t>(t0 + tt) * H + h) * dv + j0 + c] : 0.f;
-        }
-        if (tid < n) bs[tid] = bb[static_cast<int64_t>(t0 + tid) * H + h];
-        __syncthreads();
-        for (int tt = 0; tt < n; ++tt) {
-            const float* kq = ks + tt * dkp + part;
-            const float* qq = qs + tt * dkp + part;
-            const float* gq = gs + tt * dkp + part;
-            float dot = 0.f;
-#pragma unroll
-            for (int r = 0; r < KPT; ++r) {
-                S[r] *= gq[r * 4];
-                dot = fmaf(S[r], kq[r * 4], dot);
-            }
-            dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-            dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-            const float u = bs[tt] * (vs[tt * kScanCols + col] - dot);
-            float o = 0.f;
-#pragma unroll
-            for (int r = 0; r < KPT; ++r) {
-                S[r] = fmaf(kq[r * 4], u, S[r]);
-                o = fmaf(S[r], qq[r * 4], o);
-            }
-            o += __shfl_xor_sync(0xffffffffu, o, 1);
-            o += __shfl_xor_sync(0xffffffffu, o, 2);
-            if (part == 0 && j < dv) out[(static_cast<int64_t>(t0 + tt) * H + h) * dv + j] = o;
-        }
-    }
-#pragma unroll
-    for (int r = 0; r < KPT; ++r) {
-        const int i = r * 4 + part;
-        if (i < dk && j < dv) st[static_cast<int64_t>(i) * dv + j] = S[r];
-    }
-}
-
 }  // namespace cvb
 
 using namespace cvb;
 
 #define CVB_DISPATCH_KPT(dk, CALL)                  \
     do {                                            \
-        if ((dk) <= 32) { CALL(8); }                \
-        else if ((dk) <= 64) { CALL(16); }          \
-        else if ((dk) <= 128) { CALL(32); }         \
-        else { CALL(64); }                          \
+        if ((dk) <= 32) { CALL(4); }                \
+        else if ((dk) <= 64) { CALL(8); }           \
+        else if ((dk) <= 128) { CALL(16); }         \
+        else { CALL(32); }                          \
     } while (0)
 
-extern "C" int cvb_lightning_scan(float* out, const void* packed, int stride, int q_off, int k_off, int v_off, float* state,
-                                  int64_t state_floats, const float* decay, const int* cu_seqlens, const int* state_slots,
-                                  int num_slots, int S, int H, int dk, int dv, int dtype, int* err_flag, cudaStream_t stream) {
+template <int KPT, bool DELTA>
+static int launch_scan(float* out, const float* qn, const float* kn, const float* vv, const float* gg, const float* bb, const float* decay,
+                       float* state, int64_t state_floats, const int* cu_seqlens, const int* state_slots, int num_slots, int S, int H, int G,
+                       int dk, int dv, int* err_flag, cudaStream_t stream) {
+    constexpr int arrays = DELTA ? 3 : 2;
+    const size_t smem = static_cast<size_t>(2) * (arrays * kScanChunk * KPT * kScanLanes + kScanChunk * kScanCols + kScanChunk) * sizeof(float);
+    static bool raised = false;
+    if (smem > 48 * 1024 && !raised) {
+        if (cudaFuncSetAttribute(recurrent_scan_kernel<KPT, DELTA>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
+            return launch_status();
+        raised = true;
+    }
+    const dim3 grid(S, H, (dv + kScanCols - 1) / kScanCols);
+    launch_kernel(recurrent_scan_kernel<KPT, DELTA>, grid, dim3(kScanThreads), smem, stream, out, qn, kn, vv, gg, bb, decay, state,
+                  state_floats, cu_seqlens, state_slots, num_slots, H, G, dk, dv, err_flag);
+    return launch_status();
+}
+
+static bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+extern "C" int cvb_lightning_prep(float* qf, float* kf, float* vf, const void* packed, int T, int stride, int q_off, int k_off, int v_off,
+                                  int nqk, int nv, int dtype, cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || nqk <= 0 || nv <= 0) return CVB_E_SIZE;
+    if (q_off < 0 || k_off < 0 || v_off < 0 || stride < q_off + nqk || stride < k_off + nqk || stride < v_off + nv) return CVB_E_SHAPE;
+    const int64_t total = static_cast<int64_t>(T) * (2 * nqk + nv);
+    const int64_t want = (total + 255) / 256;
+    const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
+#define CALL(TY) launch_kernel(lightning_prep_kernel<TY>, dim3(blocks), dim3(256), 0, stream, qf, kf, vf, (const TY*)packed, stride, q_off, \
+                               k_off, v_off, nqk, nv, total)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_lightning_scan(float* out, const float* qf, const float* kf, const float* vf, float* state, int64_t state_floats,
+                                  const float* decay, const int* cu_seqlens, const int* state_slots, int num_slots, int S, int H, int dk,
+                                  int dv, int* err_flag, cudaStream_t stream) {
     if (S == 0) return CVB_OK;
     if (S < 0 || H <= 0 || H > 65535 || dk <= 0 || dk > 256 || dv <= 0 || num_slots <= 0) return CVB_E_SIZE;
-    if (q_off < 0 || k_off < 0 || v_off < 0 || stride < H * dk || state_floats < static_cast<int64_t>(H) * dk * dv) return CVB_E_SHAPE;
-    const dim3 grid(S, H, (dv + kScanCols - 1) / kScanCols);
-#define CALL_K(KPT)                                                                                                        \
-    do {                                                                                                                   \
-        const size_t smem = (2 * kLightChunk * KPT * 4 + kLightChunk * kScanCols) * sizeof(float);                          \
-        if (dtype == CVB_DTYPE_F32)                                                                                        \
-            launch_kernel(lightning_scan_kernel<float, KPT>, grid, dim3(kScanThreads), smem, stream, out, (const float*)packed, \
-                          stride, q_off, k_off, v_off, state, state_floats, decay, cu_seqlens, state_slots, num_slots, H, dk, dv, err_flag); \
-        else if (dtype == CVB_DTYPE_BF16)                                                                                  \
-            launch_kernel(lightning_scan_kernel<__nv_bfloat16, KPT>, grid, dim3(kScanThreads), smem, stream, out,          \
-                          (const __nv_bfloat16*)packed, stride, q_off, k_off, v_off, state, state_floats, decay, cu_seqlens, \
-                          state_slots, num_slots, H, dk, dv, err_flag);                                                    \
-        else return CVB_E_DTYPE;                                                                                           \
-    } while (0)
+    if (state_floats < static_cast<int64_t>(H) * dk * dv) return CVB_E_SHAPE;
+    if (!aligned16(qf) || !aligned16(kf) || !aligned16(vf)) return CVB_E_ALIGN;
+#define CALL_K(KPT) return launch_scan<KPT, false>(out, qf, kf, vf, nullptr, nullptr, decay, state, state_floats, cu_seqlens, state_slots, \
+                                                   num_slots, S, H, H, dk, dv, err_flag, stream)
     CVB_DISPATCH_KPT(dk, CALL_K);
 #undef CALL_K
-    return launch_status();
 }
 
 extern "C" int cvb_delta_prep(float* qn, float* kn, float* vv, float* gg, float* bb, const void* packed, int T, int stride, int qkv_off,
@@ -327,14 +358,9 @@ extern "C" int cvb_delta_scan(float* out, const float* qn, const float* kn, cons
     if (S == 0) return CVB_OK;
     if (S < 0 || H <= 0 || H > 65535 || G <= 0 || dk <= 0 || dk > 256 || dv <= 0 || num_slots <= 0) return CVB_E_SIZE;
     if (H % G || state_floats < static_cast<int64_t>(H) * dk * dv) return CVB_E_SHAPE;
-    const dim3 grid(S, H, (dv + kScanCols - 1) / kScanCols);
-#define CALL_K(KPT)                                                                                                     \
-    do {                                                                                                                \
-        const size_t smem = (3 * kDeltaChunk * KPT * 4 + kDeltaChunk * kScanCols + kDeltaChunk) * sizeof(float);          \
-        launch_kernel(delta_scan_kernel<KPT>, grid, dim3(kScanThreads), smem, stream, out, qn, kn, vv, gg, bb, state,   \
-                      state_floats, cu_seqlens, state_slots, num_slots, H, G, dk, dv, err_flag);                        \
-    } while (0)
+    if (!aligned16(qn) || !aligned16(kn) || !aligned16(vv) || !aligned16(gg)) return CVB_E_ALIGN;
+#define CALL_K(KPT) return launch_scan<KPT, true>(out, qn, kn, vv, gg, bb, nullptr, state, state_floats, cu_seqlens, state_slots, num_slots, \
+                                                  S, H, G, dk, dv, err_flag, stream)
     CVB_DISPATCH_KPT(dk, CALL_K);
 #undef CALL_K
-    return launch_status();
 }

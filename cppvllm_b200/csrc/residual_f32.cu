@@ -212,6 +212,30 @@ __global__ void bias_act_kernel(T* __restrict__ out, const T* __restrict__ x, co
     }
 }
 
+// bf16 rows whose length is a multiple of eight: eight elements per thread and step
+__global__ void bias_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ x, const float* __restrict__ bias,
+                                       int64_t n_chunks, int D, int act) {
+    pdl_trigger();
+    pdl_wait();
+    for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n_chunks;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + i * 8);
+        const __nv_bfloat162* hx = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const int c0 = static_cast<int>((i * 8) % D);
+        uint4 res;
+        __nv_bfloat162* r = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            float2 f = __bfloat1622float2(hx[k]);
+            if (bias) { f.x += bias[c0 + 2 * k]; f.y += bias[c0 + 2 * k + 1]; }
+            if (act == 1) { f.x = fmaxf(f.x, 0.f); f.x *= f.x; f.y = fmaxf(f.y, 0.f); f.y *= f.y; }
+            else if (act == 2) { f.x = gelu_tanh_of(f.x); f.y = gelu_tanh_of(f.y); }
+            r[k] = __floats2bfloat162_rn(f.x, f.y);
+        }
+        *reinterpret_cast<uint4*>(out + i * 8) = res;
+    }
+}
+
 // One block per token; a warp takes a group at a time.
 template <typename T>
 __global__ void __launch_bounds__(kUpdateThreads)
@@ -333,6 +357,13 @@ extern "C" int cvb_norm_add(float* h, const void* y, const float* bias, const fl
 extern "C" int cvb_bias_act(void* out, const void* x, const float* bias, int64_t n, int D, int act, int dtype, cudaStream_t stream) {
     if (n == 0) return CVB_OK;
     if (n < 0 || D <= 0 || act < 0 || act > 2) return CVB_E_SIZE;
+    if (dtype == CVB_DTYPE_BF16 && D % 8 == 0 && n % 8 == 0 &&
+        ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(x)) & 15) == 0) {
+        const int64_t chunks = n / 8, want8 = (chunks + 255) / 256;
+        launch_kernel(bias_act_bf16x8_kernel, dim3(static_cast<unsigned>(want8 < 148 * 16 ? want8 : 148 * 16)), dim3(256), 0, stream,
+                      (__nv_bfloat16*)out, (const __nv_bfloat16*)x, bias, chunks, D, act);
+        return launch_status();
+    }
     const int64_t want = (n + 255) / 256;
     const unsigned blocks = static_cast<unsigned>(want < 148 * 16 ? want : 148 * 16);
 #define CALL(TY) launch_kernel(bias_act_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)x, bias, n, D, act)

@@ -352,11 +352,11 @@ def dugulorn_kernel_pairs(s, pk):
     pos_b = torch.full((B,), ctx - 1, dtype=torch.int32, device=d)
     ql_b, q_b = rnd(B, H * HD), rnd(B, H * hd)
     ol_b, att_b = torch.empty(B, H * R, dtype=bf, device=d), torch.empty(B, H * hd, dtype=bf, device=d)
-    single = H <= 16
-    z = ops.attn_keys_decode_splits(B, 1, ctx) if single else 1
-    parts = torch.empty(max(1, ops.attn_keys_scratch_floats(B, 1, HD, z)), dtype=f32, device=d)
-    new = _us(lambda i: ops.attn_keys_bf16(ol_b, ql_b, lat_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B if single else ops.attn_keys_tiles([1] * B, H, 1),
-                                           H, 1, HD, page, 0.09, all_single=single, splits=z, scratch=parts if z > 1 else None, value_dim=R))
+    groups = min(n for n in range(1, H + 1) if H % n == 0 and H // n <= 16)      # heads in slabs of at most 16, as the part does
+    z = ops.attn_keys_decode_splits(B, groups, ctx)
+    parts = torch.empty(max(1, ops.attn_keys_scratch_floats(B, groups, HD, z)), dtype=f32, device=d)
+    new = _us(lambda i: ops.attn_keys_bf16(ol_b, ql_b, lat_big[i % copies], tabs[i % copies], cu_b, pos_b, B, B, H, groups, HD, page, 0.09,
+                                           all_single=True, splits=z, scratch=parts if z > 1 else None, value_dim=R, kv_heads_in_pages=1))
     splits = 4
     scratch = torch.empty(max(1, ops.attn_decode_scratch_floats(B, KV, hd, splits)), dtype=f32, device=d)
     like = _us(lambda i: ops.attn_decode_bf16(att_b, q_b, kv_big[i % copies], tabs[i % copies], cu_b, pos_b, B, H, KV, hd, page, 0.09,
@@ -370,7 +370,11 @@ def dugulorn_kernel_pairs(s, pk):
     packed = rnd(T, 4 * H * hd)
     o32 = torch.empty(T, H * hd, dtype=f32, device=d)
     decay = torch.full((H,), 0.99, dtype=f32, device=d)
-    new = _us(lambda i: ops.lightning_scan(o32, packed, 0, H * hd, 2 * H * hd, state, decay, cu, slots, 1, H, hd, hd))
+    qf, kf, vf = (torch.empty(T, H * hd, dtype=f32, device=d) for _ in range(3))
+    prep_us = _us(lambda i: ops.lightning_prep(qf, kf, vf, packed, 0, H * hd, 2 * H * hd))
+    out["lightning_prep_2048"] = {"new_us": round(prep_us, 2), "new_frac": round(T * 3 * H * hd * 6.0 / (prep_us * 1e-6) / (pk["hbm_gbs"] * 1e9), 4),
+                                  "roofline": "copy bandwidth", "note": "no like kernel in the closest model"}
+    new = _us(lambda i: ops.lightning_scan(o32, qf, kf, vf, state, decay, cu, slots, 1, H, hd, hd))
     attn_us = out["attention_prefill_2048"]["like_us"]
     out["lightning_prefill_2048"] = {"new_us": round(new, 2), "new_frac": round(4.0 * H * hd * hd * T / (new * 1e-6) / (pk["bf16_tflops"] * 1e12), 5),
                                      "like_us": attn_us, "like_frac": out["attention_prefill_2048"]["like_frac"],
@@ -395,7 +399,7 @@ def dugulorn_kernel_pairs(s, pk):
     n_copy = max(2, int(300e6 // (Bs * H * hd * hd * 4)) + 1)
     states = [torch.zeros(Bs + 1, H * hd * hd, dtype=f32, device=d) for _ in range(n_copy)]
     cu8, slots8 = torch.arange(0, Bs + 1, dtype=torch.int32, device=d), torch.arange(0, Bs, dtype=torch.int32, device=d)
-    new = _us(lambda i: ops.lightning_scan(o32[:Bs], packed[:Bs], 0, H * hd, 2 * H * hd, states[i % n_copy], decay, cu8, slots8, Bs, H, hd, hd))
+    new = _us(lambda i: ops.lightning_scan(o32[:Bs], qf[:Bs], kf[:Bs], vf[:Bs], states[i % n_copy], decay, cu8, slots8, Bs, H, hd, hd))
     like_d = out["attention_decode_b8_ctx_4096"]
     out["lightning_decode_b8"] = {"new_us": round(new, 2), "new_frac": round(Bs * H * hd * hd * 8.0 / (new * 1e-6) / (pk["hbm_gbs"] * 1e9), 4),
                                   "like_us": like_d["like_us"], "like_frac": like_d["like_frac"], "roofline": "copy bandwidth"}

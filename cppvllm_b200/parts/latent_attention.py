@@ -106,16 +106,19 @@ class LatentAttention(Mixer):
         if not self.rt.plain_kernels and R % 16 == 0 and ops.attn_keys_supported(q_att.dtype, H, 1, HD, q_att.shape[1]):
             # bf16, sizes in steps of 16 up to 128: the tensor-core kernel over keys that are values, with a narrower value
             q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * ctx.num_seqs
-            single = ctx.all_decode and ctx.num_tokens == ctx.num_seqs and H <= 16
-            splits, scratch = 1, None
-            if single:
-                splits = ops.attn_keys_decode_splits(ctx.num_seqs, 1, ctx.max_kv_len)
+            if ctx.all_decode and ctx.num_tokens == ctx.num_seqs:
+                # one token per request: the heads go in groups of at most 16 (a slab of the decode kernel), all on the one entry
+                groups = min(n for n in range(1, H + 1) if H % n == 0 and H // n <= 16)
+                splits, scratch = ops.attn_keys_decode_splits(ctx.num_seqs, groups, ctx.max_kv_len), None
                 if splits > 1:
-                    most = ops.attn_keys_scratch_floats(self.rt.workspace.max_seqs, 1, HD, 8)
-                    scratch = self.rt.workspace.flat(f"attn_keys_parts_1_{HD}", most, torch.float32)
+                    most = ops.attn_keys_scratch_floats(self.rt.workspace.max_seqs, groups, HD, 8)
+                    scratch = self.rt.workspace.flat(f"attn_keys_parts_{groups}_{HD}", most, torch.float32)
+                ops.attn_keys_bf16(o_lat, q_att, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
+                                   ctx.num_seqs, H, groups, HD, g.page_size, self.scale, all_single=True, splits=splits,
+                                   scratch=scratch, value_dim=R, kv_heads_in_pages=1)
+                return
             ops.attn_keys_bf16(o_lat, q_att, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, ctx.num_seqs,
-                               ops.attn_keys_tiles(q_lens, H, 1), H, 1, HD, g.page_size, self.scale, all_single=single,
-                               splits=splits, scratch=scratch, value_dim=R)
+                               ops.attn_keys_tiles(q_lens, H, 1), H, 1, HD, g.page_size, self.scale, value_dim=R)
             return
         ops.paged_attention_general(o_lat, q_att, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions, self.num_heads, 1,
                                     self.kv_rank + self.rot_dim, g.page_size, self.scale, num_tokens=ctx.num_tokens,

@@ -64,8 +64,11 @@ class LightningMixer(Mixer):
         H, dk, dv = self.num_heads, self.dim, self.vdim
         ws = self.rt.workspace
         packed = ops.linear(x, self.w_in, out=ws.rows("rec_in", T, self.w_in.shape[0], x.dtype))
-        o = ws.rows("rec_o", T, H * dv, torch.float32)
-        ops.lightning_scan(o, packed, 0, H * dk, 2 * H * dk, state, self.decay, ctx.cu_seqlens, ctx.state_slots, ctx.num_seqs, H, dk, dv)
+        f32 = torch.float32
+        qf, kf, vf = ws.rows("delta_q", T, H * dk, f32), ws.rows("delta_k", T, H * dk, f32), ws.rows("delta_v", T, H * dv, f32)
+        ops.lightning_prep(qf, kf, vf, packed, 0, H * dk, 2 * H * dk)
+        o = ws.rows("rec_o", T, H * dv, f32)
+        ops.lightning_scan(o, qf, kf, vf, state, self.decay, ctx.cu_seqlens, ctx.state_slots, ctx.num_seqs, H, dk, dv)
         g_off = 2 * H * dk + H * dv
         y = ops.gated_norm(ws.rows("rec_y", T, H * dv, x.dtype), o, packed[:, g_off:g_off + H * dv], self.w_norm, 1, self.eps)
         return ops.linear(y, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))

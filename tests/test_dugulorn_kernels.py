@@ -212,14 +212,17 @@ def test_attention_over_keys_whose_leading_elements_are_the_value_tensor_cores(H
     _attention_case(torch.bfloat16, H, R, dr, page, "tensor", 200 + H)
 
 
-def test_tensor_core_decode_form_with_a_narrower_value():
-    """Every request brings one token: the kernel for decoded tokens, alone and with the keys shared out among blocks."""
+@pytest.mark.parametrize("H", [8, 20, 32])
+def test_tensor_core_decode_form_with_a_narrower_value(H):
+    """Every request brings one token: the kernel for decoded tokens, alone and with the keys shared out among blocks; more
+    than 16 heads on the one stored entry go in groups."""
     ops = _ops()
-    H, R, dr, page, HD = 8, 64, 32, 32, 96
+    R, dr, page, HD = 64, 32, 32, 96
+    groups = min(n for n in range(1, H + 1) if H % n == 0 and H // n <= 16)
     lens = [700, 33, 1, 257]
     keys = [_rand(n, HD, seed=300 + i) for i, n in enumerate(lens)]
     q = _rand(4, H, HD, seed=310)
-    q[0, 3] = keys[0][5] * 8.0                       # a far key for one head
+    q[0, H - 1] = keys[0][5] * 8.0                   # a far key for one head
     q[3, 0] = keys[3][256] * 8.0                     # the token's own key, first in its page
     W = (max(lens) + page - 1) // page
     n_pages = sum((n + page - 1) // page for n in lens)
@@ -240,10 +243,10 @@ def test_tensor_core_decode_form_with_a_narrower_value():
     ref = torch.stack(ref)
     for splits in (1, 4):
         out = torch.empty(4, H * R, dtype=torch.bfloat16, device=DEV)
-        scratch = torch.empty(ops.attn_keys_scratch_floats(4, 1, HD, splits), dtype=torch.float32, device=DEV) if splits > 1 else None
+        scratch = torch.empty(ops.attn_keys_scratch_floats(4, groups, HD, splits), dtype=torch.float32, device=DEV) if splits > 1 else None
         ops.attn_keys_bf16(out, _dev(q.reshape(4, H * HD), torch.bfloat16), _dev(pages), _dev(tables), _i32([0, 1, 2, 3, 4]),
-                           _i32([n - 1 for n in lens]), 4, 4, H, 1, HD, page, 0.1, all_single=True, splits=splits, scratch=scratch,
-                           value_dim=R)
+                           _i32([n - 1 for n in lens]), 4, 4, H, groups, HD, page, 0.1, all_single=True, splits=splits, scratch=scratch,
+                           value_dim=R, kv_heads_in_pages=1)
         _close(out.reshape(4, H, R), ref, 2e-2)
 
 
@@ -259,7 +262,7 @@ def _steps(lengths_per_request):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,dk,dv", [(2, 10, 7), (1, 64, 64), (2, 130, 5), (3, 33, 50)])
+@pytest.mark.parametrize("H,dk,dv", [(2, 10, 7), (1, 64, 64), (2, 130, 5), (3, 33, 50), (2, 128, 36), (1, 256, 16)])
 def test_lightning_scan_continues_across_portions_and_slots(dtype, H, dk, dv):
     ops = _ops()
     decays = [1.0, 0.5, 0.97][:H]
@@ -280,9 +283,12 @@ def test_lightning_scan_continues_across_portions_and_slots(dtype, H, dk, dv):
                 rows.append(reqs[r][at[r]:at[r] + n]); at[r] += n
                 cu.append(cu[-1] + n); slots.append(slot_of[r])
             packed = _dev(torch.cat(rows))
-            out = torch.empty(packed.shape[0], H * dv, dtype=torch.float32, device=DEV)
-            ops.lightning_scan(out, packed, 3, 3 + H * dk, 3 + 2 * H * dk, state, _dev(torch.tensor(decays)), _i32(cu), _i32(slots),
-                               len(step), H, dk, dv)
+            n_rows = packed.shape[0]
+            out = torch.empty(n_rows, H * dv, dtype=torch.float32, device=DEV)
+            qf, kf = (torch.empty(n_rows, H * dk, dtype=torch.float32, device=DEV) for _ in range(2))
+            vf = torch.empty(n_rows, H * dv, dtype=torch.float32, device=DEV)
+            ops.lightning_prep(qf, kf, vf, packed, 3, 3 + H * dk, 3 + 2 * H * dk)
+            ops.lightning_scan(out, qf, kf, vf, state, _dev(torch.tensor(decays)), _i32(cu), _i32(slots), len(step), H, dk, dv)
             for i, (gi, n) in enumerate(step):
                 got[group[gi]].append(out[cu[i]:cu[i + 1]].cpu())
     ops.check_device_errors(torch.device(DEV))
