@@ -82,6 +82,7 @@ attn_keys_kernel(const KeysAttnParams p) {
     const int g = p.H / p.KV;
     const int tok_per_tile = kTileRows / g;
     const int kvh = blockIdx.y;
+    const int kvp = kvh / (p.KV / p.kv_phys);             // the kv head as the pages hold it
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
 
     int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
@@ -132,7 +133,7 @@ attn_keys_kernel(const KeysAttnParams p) {
                     atomicExch(p.err, 4);                 // a key a token of this block must see has no page
                     need = false;
                 } else {
-                    src = p.pages + ((static_cast<int64_t>(page) * p.kv_phys + kvh / (p.KV / p.kv_phys)) * p.page_size + off) * HD + c * 8;
+                    src = p.pages + ((static_cast<int64_t>(page) * p.kv_phys + kvp) * p.page_size + off) * HD + c * 8;
                 }
             }
             cp_async16(dst + r * LD + c * 8, src, need);
@@ -297,6 +298,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
     float* red_ml = reinterpret_cast<float*>(sK + kDecWarps * 2 * kDecKeys * LD);     // [warps][16][2]
     const int g = p.H / p.KV;
     const int seq = blockIdx.x, kvh = blockIdx.y;
+    const int kvp = kvh / (p.KV / p.kv_phys);
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int t = p.cu_seqlens[seq];
     const int pos = p.positions[t];
@@ -333,7 +335,7 @@ attn_keys_decode_kernel(const KeysAttnParams p) {
                 if (slot != last_slot) {
                     page = slot < p.table_width ? table[slot] : -1;
                     last_slot = slot;
-                    page_base = p.pages + (static_cast<int64_t>(page) * p.kv_phys + kvh / (p.KV / p.kv_phys)) * p.page_size * HD;
+                    page_base = p.pages + (static_cast<int64_t>(page) * p.kv_phys + kvp) * p.page_size * HD;
                 }
                 if (page < 0 || page >= p.num_pages) {
                     atomicExch(p.err, 4);

@@ -135,7 +135,7 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
         const float* gs = ks + kScanChunk * dkp;
         const float* vs = qs + kArrays * kScanChunk * dkp;
         const float* bs = vs + kScanChunk * kScanCols;
-        for (int tt = 0; tt < n; ++tt) {
+        auto token = [&](int tt) {
             const float* kq = ks + tt * dkp + part;
             const float* qq = qs + tt * dkp + part;
             const float v = vs[tt * kScanCols + col];
@@ -168,6 +168,12 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
 #pragma unroll
             for (int m = 1; m < kScanLanes; m <<= 1) o += __shfl_xor_sync(0xffffffffu, o, m);
             if (part == 0 && j < dv) out[(static_cast<int64_t>(t0 + tt) * H + h) * dv + j] = o;
+        };
+        if (n == kScanChunk) {                                               // unrolled: the tokens' shuffles and loads overlap
+#pragma unroll
+            for (int tt = 0; tt < kScanChunk; ++tt) token(tt);
+        } else {
+            for (int tt = 0; tt < n; ++tt) token(tt);
         }
         __syncthreads();                                                     // the stage may be filled again
     }

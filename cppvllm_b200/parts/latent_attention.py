@@ -78,18 +78,21 @@ class LatentAttention(Mixer):
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_down, self.w_uq, self.w_uk, self.w_uv, self.w_o))
 
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
+
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
         H, dn, dr, dv, R = self.num_heads, self.nope_dim, self.rot_dim, self.value_dim, self.kv_rank
         ws = self.rt.workspace
         g = ctx.groups[cache.group]
         pos = self.position
-        packed = ops.linear(x, self.w_down, out=ws.rows("lat_down", T, self.w_down.shape[0], x.dtype))
+        packed = self._project(x, self.w_down, ws.rows("lat_down", T, self.w_down.shape[0], x.dtype), T)
         cq = ws.rows("lat_cq", T, self.q_rank, x.dtype)
         writes = self.own_cache and cache.writes
         ops.latent_prep(packed, cq, 0, self.q_rank, self.w_qnorm, cache.pages if writes else None, self.kv_off, R, dr, self.rot,
                         self.w_kvnorm, pos.cos, pos.sin, ctx.positions, g.slot_mapping if writes else None, self.eps)
-        q = ops.linear(cq, self.w_uq, out=ws.rows("lat_q", T, H * (dn + dr), x.dtype))
+        q = self._project(cq, self.w_uq, ws.rows("lat_q", T, H * (dn + dr), x.dtype), T)
         q_abs = ws.rows("lat_qabs", T, H * R, x.dtype).view(H, T, R)
         torch.bmm(q.view(T, H, dn + dr)[:, :, :dn].transpose(0, 1), self.w_uk, out=q_abs)
         q_att = ops.latent_q_assemble(ws.rows("lat_qatt", T, H * (R + dr), x.dtype), q_abs, q, H, dn, R, dr, self.rot, pos.cos,
@@ -99,7 +102,7 @@ class LatentAttention(Mixer):
         o_heads = ws.rows("lat_ov", T, H * dv, x.dtype).view(H, T, dv)
         torch.bmm(o_lat.view(T, H, R).transpose(0, 1), self.w_uv, out=o_heads)
         att = ops.head_gate(ws.rows("attn_out", T, H * dv, x.dtype), o_heads, packed[:, self.g_off:self.g_off + H], H, dv)
-        return ops.linear(att, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))
+        return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
 
     def attend(self, o_lat, q_att, ctx, cache, g):
         H, HD, R = self.num_heads, self.kv_rank + self.rot_dim, self.kv_rank

@@ -22,6 +22,10 @@ from ..csrc import ops
 from .base import Mixer, StateSpec, WeightSpec, register_part
 
 
+def _project(rt, x, w, out, rows):
+    return ops.linear(x, w, out=out) if rt.plain_kernels else ops.project_rows(x, w, out, rows)
+
+
 def _cat_rows(rows):
     if len({r.dtype for r in rows}) > 1:
         rows = [r.float() for r in rows]
@@ -63,7 +67,7 @@ class LightningMixer(Mixer):
         T = x.shape[0]
         H, dk, dv = self.num_heads, self.dim, self.vdim
         ws = self.rt.workspace
-        packed = ops.linear(x, self.w_in, out=ws.rows("rec_in", T, self.w_in.shape[0], x.dtype))
+        packed = _project(self.rt, x, self.w_in, ws.rows("rec_in", T, self.w_in.shape[0], x.dtype), T)
         f32 = torch.float32
         qf, kf, vf = ws.rows("delta_q", T, H * dk, f32), ws.rows("delta_k", T, H * dk, f32), ws.rows("delta_v", T, H * dv, f32)
         ops.lightning_prep(qf, kf, vf, packed, 0, H * dk, 2 * H * dk)
@@ -71,7 +75,7 @@ class LightningMixer(Mixer):
         ops.lightning_scan(o, qf, kf, vf, state, self.decay, ctx.cu_seqlens, ctx.state_slots, ctx.num_seqs, H, dk, dv)
         g_off = 2 * H * dk + H * dv
         y = ops.gated_norm(ws.rows("rec_y", T, H * dv, x.dtype), o, packed[:, g_off:g_off + H * dv], self.w_norm, 1, self.eps)
-        return ops.linear(y, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))
+        return _project(self.rt, y, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
 
 
 @register_part("mixer", "channel_delta")
@@ -128,7 +132,7 @@ class ChannelDeltaMixer(Mixer):
         H, G, dk, dv = self.num_heads, self.num_kv_heads, self.dim, self.vdim
         ws = self.rt.workspace
         f32 = torch.float32
-        packed = ops.linear(x, self.w_in, out=ws.rows("rec_in", T, self.w_in.shape[0], x.dtype))
+        packed = _project(self.rt, x, self.w_in, ws.rows("rec_in", T, self.w_in.shape[0], x.dtype), T)
         # what enters the recurrence leaves its product unrounded
         b = ops.linear(x, self.w_b, out=ws.rows("delta_b", T, H, f32), out_dtype=f32)
         a = ops.linear(packed[:, self.a_off:self.a_off + self.decay_rank], self.w_a2, out=ws.rows("delta_a", T, H * dk, f32), out_dtype=f32)
@@ -141,4 +145,4 @@ class ChannelDeltaMixer(Mixer):
         o = ws.rows("rec_o", T, H * dv, f32)
         ops.delta_scan(o, qn, kn, vv, gg, bb, state, ctx.cu_seqlens, ctx.state_slots, S, H, G, dk, dv)
         y = ops.gated_norm(ws.rows("rec_y", T, H * dv, x.dtype), o, gate, self.w_norm, H, self.eps)
-        return ops.linear(y, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))
+        return _project(self.rt, y, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
