@@ -495,7 +495,7 @@ __global__ void attn_keys_merge_kernel(const KeysAttnParams p) {
     const int seq = blockIdx.x, kvh = blockIdx.y;
     const int t = p.cu_seqlens[seq];
     const float* base = p.parts + (static_cast<int64_t>(seq) * p.KV + kvh) * p.splits * 16 * (HD + 2);
-    for (int i = threadIdx.x; i < g * HD; i += blockDim.x) {
+    for (int i = blockIdx.z * blockDim.x + threadIdx.x; i < g * HD; i += gridDim.z * blockDim.x) {      // an element a thread
         const int r = i / HD, d = i - r * HD;
         if (d >= p.vd) continue;
         float mm = -INFINITY;
@@ -521,7 +521,7 @@ int launch_attn_keys_decode(const KeysAttnParams& p, cudaStream_t stream) {
         raised = true;
     }
     launch_kernel(attn_keys_decode_kernel<HD>, dim3(p.S, p.KV, p.splits), dim3(kDecWarps * 32), smem, stream, p);
-    if (p.splits > 1) launch_kernel(attn_keys_merge_kernel<HD>, dim3(p.S, p.KV), dim3(128), 0, stream, p);
+    if (p.splits > 1) launch_kernel(attn_keys_merge_kernel<HD>, dim3(p.S, p.KV, (p.H / p.KV * HD + 127) / 128), dim3(128), 0, stream, p);
     return launch_status();
 }
 

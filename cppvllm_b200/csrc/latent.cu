@@ -105,7 +105,7 @@ head_gate_kernel(T* __restrict__ out, const T* __restrict__ o, const T* __restri
     pdl_trigger();
     pdl_wait();
     const int64_t t = blockIdx.x;
-    for (int i = threadIdx.x; i < H * vd; i += kLatentThreads) {
+    for (int i = blockIdx.y * kLatentThreads + threadIdx.x; i < H * vd; i += gridDim.y * kLatentThreads) {
         const int h = i / vd, j = i - h * vd;
         const float z = to_float(gate[t * gate_stride + h]);
         out[t * H * vd + i] = from_float<T>(to_float(o[(static_cast<int64_t>(h) * T_total + t) * vd + j]) * (1.f / (1.f + expf(-z))));
@@ -152,7 +152,8 @@ extern "C" int cvb_head_gate(void* out, const void* o, const void* gate, int T, 
                              cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || H <= 0 || vd <= 0 || gate_stride < H) return CVB_E_SIZE;
-#define CALL(TY) launch_kernel(head_gate_kernel<TY>, dim3(T), dim3(kLatentThreads), 0, stream, (TY*)out, (const TY*)o, (const TY*)gate, \
+    const int per_row = (H * vd + kLatentThreads - 1) / kLatentThreads;
+#define CALL(TY) launch_kernel(head_gate_kernel<TY>, dim3(T, per_row < 64 ? per_row : 64), dim3(kLatentThreads), 0, stream, (TY*)out, (const TY*)o, (const TY*)gate, \
                                gate_stride, H, vd, T)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL

@@ -187,8 +187,10 @@ recurrent_scan_kernel(float* __restrict__ out, const float* __restrict__ qn, con
 
 // One block per token.  Channels: q [G * dk], k [G * dk], v [H * dv], in this order both in the packed row (from
 // column qkv_off on) and in the convolution weights [C, taps] and the history [taps - 1, C] (oldest first).
+constexpr int kPrepThreads = 512;
+
 template <typename T>
-__global__ void __launch_bounds__(kScanThreads)
+__global__ void __launch_bounds__(kPrepThreads)
 delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restrict__ vv, float* __restrict__ gg, float* __restrict__ bb,
                   const T* __restrict__ packed, int stride, int qkv_off, const float* __restrict__ conv_w, int taps,
                   const float* __restrict__ a, const float* __restrict__ dt_bias, const float* __restrict__ a_log,
@@ -209,7 +211,7 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
     }
     const int QK = G * dk, C = 2 * QK + H * dv;
     const float* hist = state + static_cast<int64_t>(slot) * state_floats + conv_off;
-    for (int c = tid; c < C; c += kScanThreads) {
+    for (int c = tid; c < C; c += kPrepThreads) {
         float acc = 0.f;
         for (int jt = 0; jt < taps; ++jt) {
             const int o = local - (taps - 1) + jt;          // which token of the portion this tap reads; negative: before it
@@ -223,7 +225,7 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
     }
     __syncthreads();
     const int warp = tid >> 5, lane = tid & 31;
-    for (int grp = warp; grp < 2 * G; grp += kScanThreads / 32) {
+    for (int grp = warp; grp < 2 * G; grp += kPrepThreads / 32) {
         const float* x = sm + grp * dk;
         float ss = 0.f;
         for (int i = lane; i < dk; i += 32) ss = fmaf(x[i], x[i], ss);
@@ -234,12 +236,12 @@ delta_prep_kernel(float* __restrict__ qn, float* __restrict__ kn, float* __restr
         else dst = kn + (t * G + (grp - G)) * dk;
         for (int i = lane; i < dk; i += 32) dst[i] = x[i] * inv;
     }
-    for (int i = tid; i < H * dk; i += kScanThreads) {
+    for (int i = tid; i < H * dk; i += kPrepThreads) {
         const float z = a[t * H * dk + i] + dt_bias[i];
         const float sp = z > 20.f ? z : log1pf(expf(z));
         gg[t * H * dk + i] = expf(-expf(a_log[i / dk]) * sp);
     }
-    for (int i = tid; i < H; i += kScanThreads) bb[t * H + i] = sigmoid_of(b[t * H + i]);
+    for (int i = tid; i < H; i += kPrepThreads) bb[t * H + i] = sigmoid_of(b[t * H + i]);
 }
 
 // One block per request; a thread owns a channel and walks its history from the oldest entry on, so that an entry is read
@@ -336,7 +338,7 @@ extern "C" int cvb_delta_prep(float* qn, float* kn, float* vv, float* gg, float*
     if (H % G || qkv_off < 0 || stride < qkv_off + C || state_floats < conv_off + (taps - 1) * C) return CVB_E_SHAPE;
     const size_t smem = static_cast<size_t>(2) * G * dk * sizeof(float);
     if (smem > 48 * 1024) return CVB_E_SIZE;
-#define CALL(TY) launch_kernel(delta_prep_kernel<TY>, dim3(T), dim3(kScanThreads), smem, stream, qn, kn, vv, gg, bb, (const TY*)packed, \
+#define CALL(TY) launch_kernel(delta_prep_kernel<TY>, dim3(T), dim3(kPrepThreads), smem, stream, qn, kn, vv, gg, bb, (const TY*)packed, \
                                stride, qkv_off, conv_w, taps, a, dt_bias, a_log, b, state, state_floats, conv_off, seq_of_token,       \
                                cu_seqlens, state_slots, num_slots, H, G, dk, dv, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);

@@ -198,6 +198,54 @@ norm_add_kernel(float* __restrict__ h, const T* __restrict__ y, const float* __r
     }
 }
 
+// Rows whose length is a multiple of four: every load is asked for before the first is used, the row stays in registers.
+template <typename T>
+__global__ void __launch_bounds__(kUpdateThreads)
+norm_add_vec_kernel(float* __restrict__ h, const T* __restrict__ y, const float* __restrict__ bias, const float* __restrict__ w,
+                    T* __restrict__ copy, int D, float eps, int accumulate) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const int n_chunks = D / 4;
+    float4 val[kUpdateChunks], old[kUpdateChunks], ww[kUpdateChunks];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kUpdateChunks; ++k) {
+        const int c = threadIdx.x + k * kUpdateThreads;
+        if (c < n_chunks) {
+            const T* py = y + row * D + c * 4;
+            float4 v = make_float4(to_float(py[0]), to_float(py[1]), to_float(py[2]), to_float(py[3]));
+            if (bias) {
+                const float4 b = *reinterpret_cast<const float4*>(bias + c * 4);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+            }
+            val[k] = v;
+            ww[k] = *reinterpret_cast<const float4*>(w + c * 4);
+            old[k] = accumulate ? *reinterpret_cast<const float4*>(h + row * D + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int k = 0; k < kUpdateChunks; ++k) {
+        const int c = threadIdx.x + k * kUpdateThreads;
+        if (c < n_chunks) {
+            float4 r;
+            r.x = old[k].x + val[k].x * inv * ww[k].x;
+            r.y = old[k].y + val[k].y * inv * ww[k].y;
+            r.z = old[k].z + val[k].z * inv * ww[k].z;
+            r.w = old[k].w + val[k].w * inv * ww[k].w;
+            *reinterpret_cast<float4*>(h + row * D + c * 4) = r;
+            if (copy) {
+                T* o = copy + row * D + c * 4;
+                o[0] = from_float<T>(r.x); o[1] = from_float<T>(r.y); o[2] = from_float<T>(r.z); o[3] = from_float<T>(r.w);
+            }
+        }
+    }
+}
+
 template <typename T>
 __global__ void bias_act_kernel(T* __restrict__ out, const T* __restrict__ x, const float* __restrict__ bias, int64_t n, int D,
                                 int act) {
@@ -236,7 +284,28 @@ __global__ void bias_act_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __
     }
 }
 
-// One block per token; a warp takes a group at a time.
+// Large groups: a block per (token, group).
+template <typename T>
+__global__ void __launch_bounds__(kUpdateThreads)
+gated_norm_block_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
+                        const float* __restrict__ w, int groups, int G, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const int g = blockIdx.y;
+    const float* og = o + (row * groups + g) * G;
+    float ss = 0.f;
+    for (int j = threadIdx.x; j < G; j += kUpdateThreads) ss = fmaf(og[j], og[j], ss);
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / static_cast<float>(G) + eps);
+    for (int j = threadIdx.x; j < G; j += kUpdateThreads) {
+        const float z = to_float(gate[row * gate_stride + g * G + j]);
+        out[(row * groups + g) * G + j] = from_float<T>(og[j] * inv * w[j] * (1.f / (1.f + expf(-z))));
+    }
+}
+
+// Small groups: a block per token and four groups; a warp takes a group.
 template <typename T>
 __global__ void __launch_bounds__(kUpdateThreads)
 gated_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __restrict__ gate, int gate_stride,
@@ -245,7 +314,7 @@ gated_norm_kernel(T* __restrict__ out, const float* __restrict__ o, const T* __r
     pdl_wait();
     const int64_t row = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = kUpdateThreads >> 5;
-    for (int g = warp; g < groups; g += n_warps) {
+    for (int g = blockIdx.y * n_warps + warp; g < groups; g += gridDim.y * n_warps) {
         const float* og = o + (row * groups + g) * G;
         float ss = 0.f;
         for (int j = lane; j < G; j += 32) ss = fmaf(og[j], og[j], ss);
@@ -347,8 +416,13 @@ extern "C" int cvb_norm_add(float* h, const void* y, const float* bias, const fl
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0) return CVB_E_SIZE;
     if (h == nullptr || y == nullptr || w == nullptr) return CVB_E_SHAPE;
-#define CALL(TY) launch_kernel(norm_add_kernel<TY>, dim3(T), dim3(kUpdateThreads), 0, stream, h, (const TY*)y, bias, w, (TY*)copy, \
-                               D, eps, accumulate)
+    auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    const bool vec_ok = D % 4 == 0 && D <= kUpdateThreads * kUpdateChunks * 4 && al(h) && al(bias) && al(w);
+#define CALL(TY)                                                                                                              \
+    if (vec_ok) launch_kernel(norm_add_vec_kernel<TY>, dim3(T), dim3(kUpdateThreads), 0, stream, h, (const TY*)y, bias, w,    \
+                              (TY*)copy, D, eps, accumulate);                                                                 \
+    else launch_kernel(norm_add_kernel<TY>, dim3(T), dim3(kUpdateThreads), 0, stream, h, (const TY*)y, bias, w, (TY*)copy,    \
+                       D, eps, accumulate)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -377,8 +451,13 @@ extern "C" int cvb_gated_norm(void* out, const float* o, const void* gate, int g
     if (T == 0) return CVB_OK;
     if (T < 0 || groups <= 0 || G <= 0) return CVB_E_SIZE;
     if (gate_stride < groups * G) return CVB_E_SHAPE;
-#define CALL(TY) launch_kernel(gated_norm_kernel<TY>, dim3(T), dim3(kUpdateThreads), 0, stream, (TY*)out, o, (const TY*)gate, \
-                               gate_stride, w, groups, G, eps)
+    if (groups > 65535) return CVB_E_SIZE;
+    const int per_block = kUpdateThreads / 32;
+#define CALL(TY)                                                                                                                 \
+    if (G > 256) launch_kernel(gated_norm_block_kernel<TY>, dim3(T, groups), dim3(kUpdateThreads), 0, stream, (TY*)out, o,       \
+                               (const TY*)gate, gate_stride, w, groups, G, eps);                                                 \
+    else launch_kernel(gated_norm_kernel<TY>, dim3(T, (groups + per_block - 1) / per_block), dim3(kUpdateThreads), 0, stream,    \
+                       (TY*)out, o, (const TY*)gate, gate_stride, w, groups, G, eps)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
