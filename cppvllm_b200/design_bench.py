@@ -53,7 +53,7 @@ def givirax_config(s, max_positions):
 
 def dugulorn_config(s, max_positions):
     D, H, hd = s["width"], s["heads"], s["dim"]
-    rot = {"dims": 32, "base": 250000.0, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}
+    rot = {"dims": 32, "base": 1.0e6, "scaling": {"factor": 8.0, "original": 4096, "fast": 16.0, "slow": 2.0}}
 
     def latent(src=None):
         m = {"heads": H, "dim": hd, "rot_dim": 32, "vdim": hd, "q_rank": 3 * D // 8, "kv_rank": 96, "scale": 1.0 / math.sqrt(hd + 32), "rot": rot}

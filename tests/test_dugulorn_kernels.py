@@ -202,12 +202,12 @@ def _attention_case(dtype, H, R, dr, page, kernel, seed):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("H,R,dr,page", [(3, 12, 8, 16), (2, 64, 32, 32), (5, 7, 3, 64)])
+@pytest.mark.parametrize("H,R,dr,page", [(3, 12, 8, 16), (2, 72, 24, 32), (5, 7, 3, 64)])
 def test_attention_over_keys_whose_leading_elements_are_the_value_general(dtype, H, R, dr, page):
     _attention_case(dtype, H, R, dr, page, "general", 100 + H)
 
 
-@pytest.mark.parametrize("H,R,dr,page", [(4, 48, 16, 32), (8, 64, 32, 32), (20, 32, 32, 16), (3, 16, 16, 64), (2, 96, 32, 32)])
+@pytest.mark.parametrize("H,R,dr,page", [(4, 48, 16, 32), (8, 80, 16, 32), (20, 32, 32, 16), (3, 16, 16, 64), (2, 96, 32, 32)])
 def test_attention_over_keys_whose_leading_elements_are_the_value_tensor_cores(H, R, dr, page):
     _attention_case(torch.bfloat16, H, R, dr, page, "tensor", 200 + H)
 
@@ -217,7 +217,7 @@ def test_tensor_core_decode_form_with_a_narrower_value(H):
     """Every request brings one token: the kernel for decoded tokens, alone and with the keys shared out among blocks; more
     than 16 heads on the one stored entry go in groups."""
     ops = _ops()
-    R, dr, page, HD = 64, 32, 32, 96
+    R, dr, page, HD = 80, 16, 32, 96
     groups = min(n for n in range(1, H + 1) if H % n == 0 and H // n <= 16)
     lens = [700, 33, 1, 257]
     keys = [_rand(n, HD, seed=300 + i) for i, n in enumerate(lens)]
