@@ -10,8 +10,8 @@
 The up-projections are taken to the query's and the output's side, so that attention runs over the cached entries
 themselves and no key or value is ever rebuilt:  q_nope . (Wuk_h c) = (Wuk_h^T q_nope) . c,  and
 sum_j a_ij Wuv_h c_j = Wuv_h (sum_j a_ij c_j).  Every head then reads the same entries: keys of kv_rank + rot_dim elements
-whose first kv_rank elements are also the value (csrc/attention_general.cu with one kv head and a value narrower than the
-key).  The two per-head products are batched library products.  The rotation turns the first ``rot`` elements of the
+whose first kv_rank elements are also the value: one kv head and a value narrower than the key, on the tensor cores
+(csrc/attention_keys.cu) for bf16 entries of up to 128 elements in steps of 16, else in csrc/attention_general.cu.  The two per-head products are batched library products.  The rotation turns the first ``rot`` elements of the
 positional parts in pairs (2i, 2i+1); the rest pass.  ``reads_other_cache``: the layer has no dkv projection and reads the
 entries another layer wrote (the run list names the unit), with its own up-projections, queries and gate.
 """

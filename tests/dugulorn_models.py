@@ -7,9 +7,9 @@
     dg_c  width 96, vocab 150: latent 20 heads 8+32/8, ranks 16/32, ff 64 | delta 3 heads, 40 x 33, 1 tap | lightning 2 x 130 x 5,
                                decays 1 and 0.5 | delta 2 heads over 2, 16 x 64, 2 taps
     dg_d  width 50, vocab 61:  lightning 1 x 33 x 50 alone
-Widths 50 and odd head sizes fit no vector width; dg_b's latent entries (48 + 16 = 64, value 48) take the tensor-core
-attention kernel, dg_a's (16 + 8) and dg_c's value of 32 + 32 with 20 heads the other forms; ranks of the delta mixers'
-low-rank projections, eps, scales and decays all differ (one decay is 1)."""
+Widths 50 and odd head sizes fit no vector width; dg_b's latent entries (48 + 16 = 64, value 48) and dg_c's (32 + 32, value 32)
+take the tensor-core attention kernel in bf16, dg_c with 20 heads in two groups when it decodes; dg_a's entries (16 + 8) take
+the general kernel; ranks of the delta mixers' low-rank projections, eps, scales and decays all differ (one decay is 1)."""
 import json
 import os
 
