@@ -107,14 +107,17 @@ class ModelRunner:
         elem = torch.empty((), dtype=dtype).element_size()
         self.page_bytes = [len(m) * cs.elements_per_token() * page_size * elem for cs, m in self.group_specs]
         self.table_width = (self.max_model_len + page_size - 1) // page_size
+        # per-request state of fixed size (recurrent mixers) is allocated behind the pages: the pool leaves room for it
+        n_slots = int(num_state_slots if num_state_slots is not None else max_seqs)
+        self.state_specs = self.model.state_specs()
+        self._state_bytes = sum((n_slots + 1) * int(np.prod(ss.shape)) * torch.empty((), dtype=ss.dtype).element_size()
+                                for ss in self.state_specs if ss is not None)
         if num_pages is None:
             num_pages = self._pages_from_free_memory(gpu_memory_utilization)
         self.num_pages = int(num_pages)
         self.storage = [torch.zeros((len(m), self.num_pages + 1) + cs.page_shape(page_size), dtype=dtype, device=self.device)
                         for cs, m in self.group_specs]
         self.scratch_page = self.num_pages                    # the extra page: padding rows of captured graphs
-        n_slots = int(num_state_slots if num_state_slots is not None else max_seqs)
-        self.state_specs = self.model.state_specs()
         if enable_prefix_caching and (len(self.group_specs) != 1 or self.group_specs[0][0].window > 0
                                       or any(ss is not None for ss in self.state_specs)):
             print("[cppvllm_b200] the prefix cache is off: it needs one group of cache units that keeps all keys and "
@@ -171,7 +174,7 @@ class ModelRunner:
         used = total_b - free_b
         cfg = self.model
         act_reserve = self.max_step_tokens * (16 * cfg.hidden_size) * 4 + self.max_seqs * cfg.vocab_size * 4 * 2 + (1 << 30)
-        budget = total_b * utilization - used - act_reserve
+        budget = total_b * utilization - used - act_reserve - getattr(self, "_state_bytes", 0)
         per_page = sum(self.page_bytes) or 1
         n = int(budget // per_page)
         if n <= 0:

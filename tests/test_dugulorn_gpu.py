@@ -190,3 +190,21 @@ def test_trace_replay_command_line(dg_dirs, tmp_path):
     portions(tb, "r", toks, sizes=(2, 5, 2, 31))
     out = run_trace(d, "float32", tb.steps, 128, str(tmp_path / "o"), ["--block-size", "16", "--state-slots", "1"])
     check(rows_by_position(tb.steps, out), {"r": plain.forward(d, toks).float()}, "float32")
+
+
+def test_the_example_command_line_with_a_pool_sized_from_free_memory(dg_dirs):
+    """`example <model_dir>`: the registry picks the design by config.json, the pool is sized from what the device has left
+    after the weights and the per-request state, and the completion is the plain implementation's."""
+    import ast
+    import os
+    import subprocess
+    import sys
+    d = dg_dirs["dg_a"]
+    prompt = dm.random_tokens(97, 9, 77)
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "example"), d, "--dtype", "float32", "--prompt", ",".join(map(str, prompt)),
+                        "--temperature", "0", "--max-tokens", "5", "--ignore-eos", "--max-num-seqs", "4", "--max-model-len", "64",
+                        "--max-num-batched-tokens", "64", "--block-size", "16"], capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0, r.stderr[-2000:]
+    line = [l for l in r.stdout.splitlines() if l.startswith("Completion:")][0]
+    assert ast.literal_eval(line[len("Completion:"):].strip()) == plain.greedy_generate(d, prompt, 5)
