@@ -89,6 +89,40 @@ def write_model(path, cfg, seed, sharpen=4.0):
     return path
 
 
+def random_config(seed):
+    """A configuration drawn at random: 2 to 6 layers of any kind in any order, with or without feed-forwards, latent layers
+    that read an earlier one's cache now and then, sizes that are odd, prime, 1 or large, every option on or off."""
+    import random
+    rng = random.Random(seed)
+    width, layers, writers = rng.choice([32, 40, 64, 72, 96, 128, 50]), [], []
+    for i in range(rng.randrange(2, 7)):
+        kind = rng.choice(["latent_attention", "lightning", "channel_delta"])
+        ff = rng.choice([None, rng.randrange(8, 200)])
+        if kind == "latent_attention":
+            if writers and rng.random() < 0.4:
+                j = rng.choice(writers)
+                m = dict(layers[j]["mixer"], kv_from=j, heads=rng.choice([1, 2, 3, 5, 8, 17]), dim=rng.choice([4, 8, 16, 24, 32]),
+                         vdim=rng.choice([4, 8, 12, 32, 40]), q_rank=rng.randrange(4, 64), scale=rng.uniform(0.05, 0.4))
+            else:
+                rot_dim = rng.choice([2, 4, 8, 16, 32, 6])
+                scaling = (rng.choice([2.0, 4.0, 1.0, 16.0]), rng.choice([16, 64, 1000]), rng.choice([32.0, 8.0, 4.0]), rng.choice([1.0, 2.0, 0.5]))
+                rot = _rot(rng.choice(range(2, rot_dim + 1, 2)), rng.choice([100.0, 10000.0, 37.5]), scaling if rng.random() < 0.6 else None)
+                m = _latent(rng.choice([1, 2, 3, 4, 8, 20]), rng.choice([4, 8, 16, 32, 64, 10]), rot_dim, rng.choice([4, 8, 16, 32, 64, 9]),
+                            rng.randrange(4, 96), rng.choice([8, 16, 32, 48, 64, 96, 20, 7]), rng.uniform(0.05, 0.4), rot)
+                writers.append(i)
+        elif kind == "lightning":
+            H = rng.choice([1, 2, 3, 6])
+            m = {"heads": H, "dim": rng.choice([4, 16, 33, 64, 100, 200]), "vdim": rng.choice([3, 16, 32, 40, 70]),
+                 "decay": [rng.choice([1.0, 0.999, 0.9, 0.6, rng.uniform(0.3, 1.0)]) for _ in range(H)]}
+        else:
+            G = rng.choice([1, 2, 3])
+            m = {"heads": G * rng.choice([1, 2, 3]), "kv_heads": G, "dim": rng.choice([4, 16, 32, 48, 64, 130]), "vdim": rng.choice([4, 16, 32, 64, 33]),
+                 "conv": rng.choice([1, 2, 3, 4, 5]), "a_rank": rng.randrange(2, 30), "g_rank": rng.randrange(2, 30)}
+        layers.append(_layer(kind, m, ff))
+    return {"architecture": "Dugulorn", "vocab": rng.randrange(40, 300), "width": width, "norm": {"eps": rng.choice([1e-5, 1e-6, 1e-3])},
+            "layers": layers}
+
+
 def write_all(base):
     return {name: write_model(os.path.join(base, name), cfg, seed) for name, (cfg, seed, _) in SETUPS.items()}
 

@@ -69,6 +69,26 @@ def test_whole_tail_and_portions_match_the_plain_implementation(dg_dirs, name, d
     assert all(runner.cache.num_free_pages(g) == 128 // dm.page_size(name) for g in range(len(runner.group_specs)))
 
 
+@pytest.mark.parametrize("seed", range(100, 110))
+def test_configurations_drawn_at_random(tmp_path, seed):
+    """Layers of every kind in any order and size (tests/dugulorn_models.py: random_config): a whole prompt, a tail decoded
+    token by token and portions down to two tokens, in float32, where nothing but the order of sums may differ."""
+    import random
+    cfg = dm.random_config(seed)
+    d = dm.write_model(str(tmp_path / "m"), cfg, seed)
+    toks = {"w": dm.random_tokens(cfg["vocab"], 90, 1), "t": dm.random_tokens(cfg["vocab"], 75, 2), "p": dm.random_tokens(cfg["vocab"], 90, 1)}
+    tb = TraceBuilder()
+    whole(tb, "w", toks["w"])
+    tail_one_by_one(tb, "t", toks["t"], tail=20)
+    portions(tb, "p", toks["p"])
+    from cppvllm_b200.engine.runner import ModelRunner
+    page = random.Random(seed).choice([16, 32, 64])
+    runner = ModelRunner(d, dtype=torch.float32, page_size=page, num_pages=128 // page, max_step_tokens=128, max_seqs=4, max_model_len=128,
+                         num_state_slots=2)
+    rows = rows_by_position(tb.steps, run_trace_in_process(runner, tb.steps))
+    check(rows, {k: plain.forward(d, v).float() for k, v in toks.items()}, "float32")
+
+
 @pytest.mark.parametrize("dtype,eager", [("float32", False), ("bfloat16", False), ("float32", True)])
 @pytest.mark.parametrize("name", ["dg_a", "dg_b", "dg_c"])
 def test_unequal_requests_in_one_batch_with_pages_and_slots_used_again(dg_dirs, name, dtype, eager):
